@@ -125,8 +125,11 @@ class RequestCache:
 
 
 def _cache_id_order(cache_id):
-    """Cache ids are layer indices, or (layer, sub-id) for a layer with several mixers: ordered by layer."""
-    return (cache_id, "") if isinstance(cache_id, int) else (cache_id[0], str(cache_id[1]))
+    """Cache ids are layer indices, (layer, sub-id) for a layer with several mixers, or (layer, sub-id, instance) for the
+    later runs of a layer that runs several times with caches of its own: ordered by layer, then instance."""
+    if isinstance(cache_id, int):
+        return (cache_id, 0, "")
+    return (cache_id[0], int(cache_id[2]) if len(cache_id) > 2 else 0, str(cache_id[1]))
 
 
 def group_needs(needs: Mapping[object, Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[object]]]:

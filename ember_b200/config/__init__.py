@@ -1,5 +1,5 @@
 """Typed configurations and the architecture registry."""
-from .spec import (AttentionSpec, ConfigError, GatedDeltaSpec, GatedLinearAttentionSpec, GatedMLPSpec, LatentAttentionSpec,
+from .spec import (AttentionSpec, ConfigError, DynamicTanhSpec, HyperConnectionSpec, TimeMixSpec, GatedDeltaSpec, GatedLinearAttentionSpec, GatedMLPSpec, LatentAttentionSpec,
                    LayerNormSpec, LayerSpec, MatrixMemorySpec, ModelSpec, NoPositionSpec, ParallelMixerSpec, PartSpec,
                    RMSNormSpec, RotarySpec, RoutedMLPSpec, ScheduleEntry, SigmoidAttentionSpec, SigmoidGateSpec,
                    SinkAttentionSpec, StateSpaceSpec, default_schedule)
@@ -8,6 +8,7 @@ from .registry import (config_from_dict, load_config, load_model_spec, register_
 from .qwen3 import Qwen3Config
 from .fadosun import FadosunConfig
 from .zufusun import ZufusunConfig
+from .fomanex import FomanexConfig
 
 __all__ = [
     "AttentionSpec", "ConfigError", "GatedMLPSpec", "LayerSpec", "ModelSpec", "NoPositionSpec", "PartSpec",
@@ -15,5 +16,6 @@ __all__ = [
     "load_model_spec", "register_architecture", "registered_architectures", "resolve_architecture",
     "Qwen3Config", "FadosunConfig", "GatedDeltaSpec", "LayerNormSpec", "MatrixMemorySpec", "ParallelMixerSpec",
     "SigmoidAttentionSpec", "SigmoidGateSpec", "StateSpaceSpec", "ZufusunConfig", "GatedLinearAttentionSpec",
-    "LatentAttentionSpec", "RoutedMLPSpec", "SinkAttentionSpec",
+    "LatentAttentionSpec", "RoutedMLPSpec", "SinkAttentionSpec", "FomanexConfig", "DynamicTanhSpec", "HyperConnectionSpec",
+    "TimeMixSpec",
 ]

@@ -51,6 +51,18 @@ class LayerNormSpec(PartSpec):
     bias_suffix: str = "bias"
 
 
+@dataclass(frozen=True)
+class DynamicTanhSpec(PartSpec):
+    """out = tanh(alpha * x) * weight + bias, element by element: a norm that takes no mean or variance.  ``alpha`` is a
+    stored scalar.  The tensors are named prefix + ``weight_suffix``, ``bias_suffix`` and ``alpha_suffix``."""
+
+    kind: ClassVar[str] = "dynamic_tanh"
+    size: int = 0
+    weight_suffix: str = "weight"
+    bias_suffix: str = "bias"
+    alpha_suffix: str = "alpha"
+
+
 # ---------------------------------------------------------------- position encodings
 @dataclass(frozen=True)
 class RotarySpec(PartSpec):
@@ -66,6 +78,14 @@ class RotarySpec(PartSpec):
     # in double precision, rounded once
     frequency_precision: str = "float32"
     layout: str = "half"
+    # Stretching for contexts longer than the model was made for (YaRN): with d(t) = rotary_dim ln(original / (2 pi t)) /
+    # (2 ln theta), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and the ramp
+    # r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes f_i / factor * r_i + f_i (1 - r_i), and
+    # cosines and sines are multiplied by 0.1 ln(factor) + 1.  ``scaling_factor`` 0: no stretching.
+    scaling_factor: float = 0.0
+    scaling_original: float = 0.0
+    scaling_fast: float = 32.0
+    scaling_slow: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -149,7 +169,8 @@ class LatentAttentionSpec(PartSpec):
     RMS-normed, is the latent c; the rest, rotated, is a key part all heads share.  Per head the unrotated key is
     W_uk c and the value W_uv c; only [c | rotated part] is cached.  A sink per head joins the softmax's denominator,
     and the concatenated heads are multiplied by sigmoid(W_g h) before W_o.  ``own_kv`` False: the layer has no W_dkv
-    and reads the cache of another layer (the schedule says whose)."""
+    and reads the cache of another layer (the schedule says whose).  ``q_rank`` 0: no query latent, q = W_q h (tensor
+    ``q``).  The rotated parts follow ``position`` (its layout, frequencies and magnitude)."""
 
     kind: ClassVar[str] = "latent_attention"
     hidden_size: int = 0
@@ -181,6 +202,22 @@ class GatedLinearAttentionSpec(PartSpec):
     tau: float = 16.0
     decay_rank: int = 0
     norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class TimeMixSpec(PartSpec):
+    """Time mixing with a matrix state per head and a decay per head and key channel (RWKV style).  With h' the
+    previous token's input (zeros before the first token; part of the state), each of r, k, v, g, w reads its own blend
+    h + (h' - h) mu; r, k, v are heads x head_dim, the gate is silu(W_g .), the decay
+    w = exp(-exp(W_w2 tanh(W_w1 .) + w0)).  Per head: o = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T; o is divided
+    by its root mean square, times ``norm``, times the gate, W_o.  ``decay_rank`` 0: read from the stored tensors' shapes."""
+
+    kind: ClassVar[str] = "wkv"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    decay_rank: int = 0
+    norm_eps: float = 1e-5
 
 
 @dataclass(frozen=True)
@@ -265,8 +302,8 @@ class SigmoidGateSpec(PartSpec):
 # --------------------------------------------------------------------- feed-forwards
 @dataclass(frozen=True)
 class GatedMLPSpec(PartSpec):
-    """down( act(gate(x)) * up(x) ), no biases; act is "silu" or "relu".  ``names``: the three tensors' names under
-    the prefix (gate, up, down)."""
+    """down( act(gate(x)) * up(x) ), no biases; act is "silu", "relu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2 / pi)
+    (z + 0.044715 z^3)))).  ``names``: the three tensors' names under the prefix (gate, up, down)."""
 
     kind: ClassVar[str] = "gated_mlp"
     hidden_size: int = 0
@@ -288,6 +325,36 @@ class RoutedMLPSpec(PartSpec):
     top: int = 0
     limit: float = 7.0
     alpha: float = 1.702
+    # ``limit`` 0: no clamps.  ``up_offset``: what is added to the (clamped) up projection, so that limit 0, alpha 1
+    # and up_offset 0 give silu(W_gate h) * W_up h.
+    up_offset: float = 1.0
+    # ``scoring`` "softmax_top" as above, or "sigmoid": scores s = sigmoid(logits); the choice is by s + correction
+    # (tensor ``correction`` [experts], if ``correction``), the weights are the chosen experts' s times
+    # ``route_scale``, divided by their sum if ``renormalize``.
+    scoring: str = "softmax_top"
+    correction: bool = False
+    route_scale: float = 1.0
+    renormalize: bool = False
+
+
+# ---------------------------------------------------------------------- connections
+@dataclass(frozen=True)
+class HyperConnectionSpec(PartSpec):
+    """How a sublayer reads from and writes to ``streams`` copies x_1 .. x_s of the residual stream: its input is
+    u = sum_s in[s] x_s, and with its result y all streams change at once from the old ones,
+    x_t <- sum_s mix[s, t] x_s + multiplier * out[t] * (scale * y) (``mix`` is indexed [from, to]; ``scale`` a vector over
+    the width, element by element, if ``layer_scale``).  Tensors: prefix + ``name`` + ".in" [s], ".out" [s], ".mix"
+    [s, s], and prefix + ``scale_name`` [size].  ``learned`` False: no tensors, in = out = 1 and mix the identity (with
+    one stream, the plain residual sum x <- x + multiplier * scale * y)."""
+
+    kind: ClassVar[str] = "hyper"
+    size: int = 0
+    streams: int = 1
+    multiplier: float = 1.0
+    layer_scale: bool = False
+    learned: bool = True
+    name: str = "hc"
+    scale_name: str = "ls"
 
 
 # ---------------------------------------------------------------------------- layers
@@ -331,10 +398,12 @@ class LayerSpec:
 class ScheduleEntry:
     """One position in the run order.  ``layer`` indexes ``ModelSpec.layers``; a layer
     may appear more than once.  ``cache_of`` names the layer whose cache this run
-    reads and writes; -1 means its own."""
+    reads and writes; -1 means its own.  ``instance`` tells the caches of one layer apart: a layer
+    that runs several times with the same weights (a loop) keeps one cache or state per pass."""
 
     layer: int
     cache_of: int = -1
+    instance: int = 0
 
 
 @dataclass(frozen=True)
@@ -362,6 +431,15 @@ class ModelSpec:
     # decoders scale the embedded tokens by sqrt(hidden) or the logits by a constant
     embedding_multiplier: float = 1.0
     logit_scale: float = 1.0
+    # a norm on the embedded (and scaled) tokens, before the first layer
+    embedding_norm: Optional[PartSpec] = None
+    embedding_norm_prefix: str = "model.embed_norm."
+    # logits <- cap * tanh(logits / cap), after the logit scale (which is then applied to the fp32 logits themselves, not
+    # folded into the final norm); 0: none
+    logit_softcap: float = 0.0
+    # the residual stream in ``residual_streams`` copies (hyper-connections): all equal to the embedding's output at the
+    # start, read and written by the layers' connections, summed before the final norm
+    residual_streams: int = 1
 
     def __post_init__(self):
         n = len(self.layers)
@@ -374,6 +452,10 @@ class ModelSpec:
                 raise ConfigError(f"schedule names layer {e.layer}; the model has {n}")
             if not (-1 <= e.cache_of < n):
                 raise ConfigError(f"schedule entry reads the cache of layer {e.cache_of}; the model has {n}")
+            if e.instance < 0:
+                raise ConfigError("a schedule entry's cache instance cannot be negative")
+        if self.residual_streams < 1:
+            raise ConfigError("a model has at least one residual stream")
 
 
 def default_schedule(n_layers: int) -> Tuple[ScheduleEntry, ...]:

@@ -9,7 +9,7 @@
 // Epilogues (the reference's are src/backend/cuda/k_gemm.cu:29-53):
 //   0 store in the activation dtype      1 store fp32
 //   2 add into an fp32 matrix (residual) 3 silu(c[2j]) * c[2j+1] over interleaved gate/up rows
-//   6 relu(c[2j]) * c[2j+1] likewise
+//   6 relu(c[2j]) * c[2j+1] likewise     7 gelu(c[2j]) * c[2j+1], gelu in its tanh form
 // An optional fp32 bias[N] is added before the epilogue.
 #include "common.cuh"
 
@@ -80,7 +80,9 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, in
             } else {
                 if ((j & 1) == 0) {  // n even: gate; n + 1: up (same thread, N is even)
                     const float u = acc[i][j + 1] + (bias ? bias[n + 1] : 0.0f);
-                    ((TA*)Cv)[(size_t)m * ldc + (n >> 1)] = from_float<TA>((EPI == 6 ? fmaxf(c, 0.0f) : c / (1.0f + expf(-c))) * u);
+                    const float a = EPI == 6 ? fmaxf(c, 0.0f)
+                                  : (EPI == 7 ? 0.5f * c * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * c * c, c, c))) : c / (1.0f + expf(-c)));
+                    ((TA*)Cv)[(size_t)m * ldc + (n >> 1)] = from_float<TA>(a * u);
                 }
             }
         }
@@ -99,6 +101,7 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, vo
         case 2: launch_kernel(gemm_simt_kernel<TA, TW, 2>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
         case 3: launch_kernel(gemm_simt_kernel<TA, TW, 3>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
         case 6: launch_kernel(gemm_simt_kernel<TA, TW, 6>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
+        case 7: launch_kernel(gemm_simt_kernel<TA, TW, 7>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
         default: return fail("gemm: unknown epilogue %d", epi);
     }
     return check_launch("gemm_simt");
@@ -113,7 +116,7 @@ EMBER_API int ember_gemm_simt(const void* A, int a_dtype, int lda, const void* W
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) return fail("gemm: K=%d", K);
     if (lda < K || ldw < K) return fail("gemm: row strides (%d, %d) smaller than K=%d", lda, ldw, K);
-    const bool gated = epilogue == 3 || epilogue == 6;
+    const bool gated = epilogue == 3 || epilogue == 6 || epilogue == 7;
     if (gated && (N & 1)) return fail("gemm: the gated epilogue needs an even N, got %d", N);
     if (ldc < (gated ? N / 2 : N)) return fail("gemm: output stride %d too small for N=%d", ldc, N);
     if ((M + BM - 1) / BM > 65535) return fail("gemm: M=%d is too large for one launch", M);

@@ -220,7 +220,7 @@ using namespace ember;
 EMBER_API int ember_gemm_tc_supported(int M, int N, int K, int epilogue) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8) return 0;                       // TMA needs 16-byte row pitch
-    if ((epilogue == 3 || epilogue == 6) && (N & 1)) return 0;       // 6: the gated epilogue with relu
+    if ((epilogue == 3 || epilogue == 6 || epilogue == 7) && (N & 1)) return 0;       // 6, 7: the gated epilogue with relu, gelu
     if (epilogue == 5 && M > 128) return 0;    // the sums stay in the scratch of the small-M product
     return 1;
 }
@@ -237,8 +237,8 @@ EMBER_API long long ember_gemm_tc_scratch_floats(int max_tokens_swapped, int N) 
 EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, int M, int N, int K, int epilogue,
                             float* scratch, long long scratch_floats, int num_sms, int split_mode, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
-    const int act = epilogue == 6 ? 1 : 0;             // epilogue 6: relu(gate) * up, the gated epilogue with another activation
-    if (epilogue == 6) epilogue = 3;
+    const int act = epilogue == 6 ? 1 : (epilogue == 7 ? 2 : 0);      // epilogues 6, 7: the gated epilogue with relu, with gelu (tanh form)
+    if (epilogue == 6 || epilogue == 7) epilogue = 3;
     const bool sums = epilogue == 5;
     if (sums) {
         if (M > 128 || !scratch || scratch_floats < (long long)M * N)

@@ -46,7 +46,7 @@ struct GemmTcParams {
     int num_k_blocks;     // ceil(K / TILE_K)
     int k_blocks_per_split;
     int epilogue;         // 0 store bf16, 1 store fp32, 2 add fp32, 3 act(gate)*up -> bf16
-    int act;              // epilogue 3: 0 silu, 1 relu
+    int act;              // epilogue 3: 0 silu, 1 relu, 2 gelu (tanh form)
     void* out;
     int ldc;
     float* accum;         // atomic split-K target: fp32 [M, accum_ld] (the residual itself for epilogue 2)
@@ -141,7 +141,9 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(int n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
 }
 
-__device__ __forceinline__ float gate_mul(float g, float u, int act) {      // act(gate) * up: act 0 silu, 1 relu
+// act(gate) * up: act 0 silu, 1 relu, 2 gelu in its tanh form, 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3)))
+__device__ __forceinline__ float gate_mul(float g, float u, int act) {
+    if (act == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * g * g, g, g))) * u;
     return (act ? fmaxf(g, 0.0f) : g / (1.0f + __expf(-g))) * u;
 }
 

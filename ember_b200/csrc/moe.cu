@@ -28,12 +28,19 @@ namespace ember {
 constexpr int MOE_MAX_EXPERTS = 256;
 constexpr int MOE_BM = 32, MOE_BN = 64, MOE_BK = 16;
 
+// How the chosen experts are found and weighed.  sigmoid 0: by the logits, weights = softmax over the chosen logits
+// alone.  sigmoid 1: scores s = sigmoid(logit); the choice is by s + correction[e] (correction may be null), the
+// weights are the chosen experts' s times scale, divided by their sum first if renormalize.
+struct RouteRule {
+    int sigmoid; const float* correction; float scale; int renormalize;
+};
+
 // One warp a token.  A lane holds experts lane, lane + 32, ... in z.
 __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32], int E, int top, int* __restrict__ sel,
-                                               float* __restrict__ wgt, int t, int lane);
+                                               float* __restrict__ wgt, int t, int lane, const RouteRule& rule);
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int top, int* __restrict__ sel,
-                                 float* __restrict__ wgt, int T) {
+                                 float* __restrict__ wgt, int T, RouteRule rule) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -44,14 +51,15 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
         const int e = lane + 32 * i;
         z[i] = e < E ? logits[(size_t)t * E + e] : -INFINITY;
     }
-    choose_experts(z, E, top, sel, wgt, t, lane);
+    choose_experts(z, E, top, sel, wgt, t, lane, rule);
 }
 
 // The router's product and the choice in one: logits[e] = sum_k x[t, k] w[e, k] with fp32 weights and sums.  A block
 // a token: its warps share the experts (four elements a lane and load), the first warp then chooses.
 template <typename T>
 __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int K, int E, int top,
-                                                         int* __restrict__ sel, float* __restrict__ wgt, float* __restrict__ logits) {
+                                                         int* __restrict__ sel, float* __restrict__ wgt, float* __restrict__ logits,
+                                                         RouteRule rule) {
     __shared__ float zs[MOE_MAX_EXPERTS];
     pdl_launch_dependents();
     pdl_wait();
@@ -84,11 +92,20 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x
         const int e = lane + 32 * i;
         z[i] = e < E ? zs[e] : -INFINITY;
     }
-    choose_experts(z, E, top, sel, wgt, t, lane);
+    choose_experts(z, E, top, sel, wgt, t, lane, rule);
 }
 
 __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32], int E, int top, int* __restrict__ sel,
-                                               float* __restrict__ wgt, int t, int lane) {
+                                               float* __restrict__ wgt, int t, int lane, const RouteRule& rule) {
+    float score[MOE_MAX_EXPERTS / 32];                      // sigmoid rule: s of the lane's experts; z becomes what is compared
+    if (rule.sigmoid) {
+#pragma unroll
+        for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+            const int e = lane + 32 * i;
+            score[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.0f;
+            if (e < E) z[i] = score[i] + (rule.correction ? rule.correction[e] : 0.0f);
+        }
+    }
     float first = 0.0f, sum = 0.0f, mine = 0.0f;            // lane k keeps the k-th choice's weight (top <= 32)
     for (int k = 0; k < top; k++) {
         float best = -INFINITY;
@@ -106,7 +123,16 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
         }
         if (at == 0x7fffffff) { at = 0; best = first; }     // (no finite logit left: only with NaNs in the row)
         if (k == 0) first = best;
-        const float w = expf(best - first);
+        float w;
+        if (rule.sigmoid) {                                 // the chosen expert's own score, from the lane that holds it
+            float sc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+                if (i == (at >> 5)) sc = score[i];
+            w = __shfl_sync(0xffffffffu, sc, at & 31);
+        } else {
+            w = expf(best - first);
+        }
         sum += w;
         if (lane == k) mine = w;
         if (lane == 0) sel[(size_t)t * top + k] = at;
@@ -116,7 +142,10 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
                 if (i == (at >> 5)) z[i] = -INFINITY;
         }
     }
-    if (lane < top) wgt[(size_t)t * top + lane] = mine / sum;
+    if (lane < top) {
+        if (rule.sigmoid) wgt[(size_t)t * top + lane] = (rule.renormalize ? mine / sum : mine) * rule.scale;
+        else wgt[(size_t)t * top + lane] = mine / sum;
+    }
 }
 
 // One block.  counts / offsets by expert, slots by atomic cursors, then the row tiles.
@@ -170,7 +199,7 @@ struct MoeGemmArgs {
     const int* offsets; const int* pair_of_slot; const int* n_tiles; const int* tile_expert; const int* tile_row0;
     int top;                             // > 0: row of x = pair / top (a token); 0: row of x = slot
     int N, K;
-    float limit, alpha;
+    float limit, alpha, up_offset;      // (limit may be +inf: no clamps)
 };
 
 // GATED: N counts interleaved (gate, up) rows, the output has N / 2 columns.
@@ -231,7 +260,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs p) {
                 if (n >= p.N) continue;
                 const float g = fminf(acc[i][j], p.limit);
                 const float u = fminf(fmaxf(acc[i][j + 1], -p.limit), p.limit);
-                o[n >> 1] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + 1.0f));
+                o[n >> 1] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + p.up_offset));
             }
         } else {
 #pragma unroll
@@ -304,7 +333,7 @@ __device__ __forceinline__ void moe_stream_rows(const MoeGemmArgs& p, const uint
             TO* o = (TO*)p.out + (size_t)(row0 + lane) * p.ld_o;
             if (GATED) {
                 const float g = fminf(v0, p.limit), u = fminf(fmaxf(v1, -p.limit), p.limit);
-                o[pr] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + 1.0f));
+                o[pr] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + p.up_offset));
             } else {
                 o[n0] = from_float<TO>(v0);
                 if (two) o[n0 + 1] = from_float<TO>(v1);
@@ -431,7 +460,7 @@ __global__ void __launch_bounds__(MT_WARPS * 32) moe_stream_tc_kernel(MoeGemmArg
                     const float up = __shfl_xor_sync(0xffffffffu, v, 4);     // the odd row beside this even one
                     if ((g & 1) == 0 && n < p.N && slot < rows) {
                         const float gt = fminf(v, p.limit), u = fminf(fmaxf(up, -p.limit), p.limit);
-                        ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + (n >> 1)] = from_float<TO>(gt / (1.0f + expf(-p.alpha * gt)) * (u + 1.0f));
+                        ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + (n >> 1)] = from_float<TO>(gt / (1.0f + expf(-p.alpha * gt)) * (u + p.up_offset));
                     }
                 } else if (n < p.N && slot < rows) {
                     ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + n] = from_float<TO>(v);
@@ -452,14 +481,15 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __rest
 
 // act[slot, j] = g sigmoid(alpha g) (u + 1), g = min(gu[slot, 2j], limit), u = clamp(gu[slot, 2j + 1], -limit, limit).
 template <typename TO>
-__global__ void moe_activation_kernel(const float2* __restrict__ gu, TO* __restrict__ act, size_t n, float limit, float alpha) {
+__global__ void moe_activation_kernel(const float2* __restrict__ gu, TO* __restrict__ act, size_t n, float limit, float alpha,
+                                      float up_offset) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const float2 v = gu[i];
     const float g = fminf(v.x, limit), u = fminf(fmaxf(v.y, -limit), limit);
-    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + up_offset));
 }
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ slot_of_pair,
@@ -481,24 +511,27 @@ using namespace ember;
 
 EMBER_API int ember_moe_tile_rows() { return MOE_BM; }
 
-EMBER_API int ember_moe_route(const float* logits, int T, int E, int top, int* sel, float* wgt, void* stream) {
+EMBER_API int ember_moe_route(const float* logits, int T, int E, int top, int* sel, float* wgt, int sigmoid, const float* correction,
+                              float scale, int renormalize, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32)
         return fail("moe_route: top %d of %d experts (at most 32 of %d)", top, E, MOE_MAX_EXPERTS);
-    launch_kernel(moe_route_kernel, (unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream, logits, E, top, sel, wgt, T);
+    launch_kernel(moe_route_kernel, (unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream, logits, E, top, sel, wgt, T,
+                  RouteRule{sigmoid, correction, scale, renormalize});
     return check_launch("moe_route");
 }
 
 EMBER_API int ember_moe_router(const void* x, int x_dtype, const float* w, int T, int K, int E, int top, int* sel, float* wgt,
-                               float* logits, void* stream) {
+                               float* logits, int sigmoid, const float* correction, float scale, int renormalize, void* stream) {
     if (T <= 0) return 0;
+    const RouteRule rule{sigmoid, correction, scale, renormalize};
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32 || K <= 0)
         return fail("moe_router: top %d of %d experts (at most 32 of %d), rows of %d", top, E, MOE_MAX_EXPERTS, K);
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned threads = E >= 8 ? 256 : 32 * E;           // a warp an expert, up to eight
-    if (x_dtype == EMBER_F32) launch_kernel(moe_router_kernel<float>, T, threads, 0, st, (const float*)x, w, K, E, top, sel, wgt, logits);
+    if (x_dtype == EMBER_F32) launch_kernel(moe_router_kernel<float>, T, threads, 0, st, (const float*)x, w, K, E, top, sel, wgt, logits, rule);
     else if (x_dtype == EMBER_BF16)
-        launch_kernel(moe_router_kernel<__nv_bfloat16>, T, threads, 0, st, (const __nv_bfloat16*)x, w, K, E, top, sel, wgt, logits);
+        launch_kernel(moe_router_kernel<__nv_bfloat16>, T, threads, 0, st, (const __nv_bfloat16*)x, w, K, E, top, sel, wgt, logits, rule);
     else return fail("moe_router: unsupported dtype %d", x_dtype);
     return check_launch("moe_router");
 }
@@ -516,10 +549,10 @@ EMBER_API int ember_moe_group(const int* sel, int n_pairs, int E, int* offsets, 
 EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
                              int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
                              const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
-                             float limit, float alpha, void* stream) {
+                             float limit, float alpha, float up_offset, void* stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_gemm: N=%d K=%d", N, K);
-    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha};
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset};
     dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
     cudaStream_t st = (cudaStream_t)stream;
     const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
@@ -542,14 +575,14 @@ EMBER_API int ember_moe_stream_rows() { return MS_ROWS; }
 EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
                                int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
                                const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
-                               float limit, float alpha, void* stream) {
+                               float limit, float alpha, float up_offset, void* stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_stream: N=%d K=%d", N, K);
     const int elem = x_dtype == EMBER_F32 ? 4 : 2;
     if (((size_t)K * elem) % 16 || ((size_t)ld_x * elem) % 16) return fail("moe_stream: rows of %d elements are no multiple of 16 bytes", K);
     const size_t smem = (size_t)MS_ROWS * K * elem;
     if (smem > 200 * 1024) return fail("moe_stream: %d rows of %d do not fit in shared memory", MS_ROWS, K);
-    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha};
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset};
     cudaStream_t st = (cudaStream_t)stream;
     const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
     static int tc_on = -1;
@@ -587,13 +620,14 @@ EMBER_API int ember_moe_gather(const void* x, const int* pair_of_slot, int n_pai
     return check_launch("moe_gather");
 }
 
-EMBER_API int ember_moe_activation(const float* gu, void* act, int out_dtype, long long n, float limit, float alpha, void* stream) {
+EMBER_API int ember_moe_activation(const float* gu, void* act, int out_dtype, long long n, float limit, float alpha, float up_offset,
+                                   void* stream) {
     if (n <= 0) return 0;
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (out_dtype == EMBER_F32) launch_kernel(moe_activation_kernel<float>, blocks, 256, 0, st, (const float2*)gu, (float*)act, (size_t)n, limit, alpha);
+    if (out_dtype == EMBER_F32) launch_kernel(moe_activation_kernel<float>, blocks, 256, 0, st, (const float2*)gu, (float*)act, (size_t)n, limit, alpha, up_offset);
     else if (out_dtype == EMBER_BF16)
-        launch_kernel(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const float2*)gu, (__nv_bfloat16*)act, (size_t)n, limit, alpha);
+        launch_kernel(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const float2*)gu, (__nv_bfloat16*)act, (size_t)n, limit, alpha, up_offset);
     else return fail("moe_activation: unsupported dtype %d", out_dtype);
     return check_launch("moe_activation");
 }

@@ -6,6 +6,11 @@
 //   group_norm_gate   a token's row cut into groups, each divided by its own root mean square, times a weight,
 //                     with a gate before (silu) or after (sigmoid or silu) the norm
 //   scaled_sum        out (+)= a x + b y
+//   dynamic_tanh      out = tanh(alpha x) * w + b, element by element (a norm without statistics)
+//   stream_read       u = sum_s in[s] x_s over the copies of the residual stream (optionally through dynamic_tanh)
+//   stream_write      x_t <- sum_s mix[s, t] x_s + multiplier * out[t] * scale * y, all copies at once from the old ones
+//   stream_spread     every copy = one row;   stream_sum   one row = the sum of the copies
+//   logit_finish      logits <- cap tanh(scale logits / cap)
 // Rows are read from the fp32 residual stream or from fp32 results of a product; a row is reduced by one block
 // (or one warp for the short rows of a head) in an order fixed by the thread layout.
 #include "common.cuh"
@@ -134,6 +139,110 @@ __global__ void scaled_sum_kernel(const float* __restrict__ x, float a, const fl
     out[i] = accumulate ? out[i] + v : v;
 }
 
+
+// ------------------------------------------------------------------------------------------ dynamic tanh
+// out[r, i] = (tanh(alpha x[rows[r] or r, i]) * w[i] + b[i]); alpha is a stored scalar (read from the device).
+template <typename TO>
+__global__ void dynamic_tanh_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ alpha,
+                                    const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ out, int H, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const size_t r = idx / H;
+    const int i = (int)(idx - r * H);
+    const float v = x[(size_t)(rows ? rows[r] : r) * H + i];
+    out[idx] = from_float<TO>(fmaf(tanhf(alpha[0] * v), w[i], b ? b[i] : 0.0f));
+}
+
+// ------------------------------------------------------------------- several copies of the residual stream
+// X is [T, S, H] fp32.  A sublayer reads u = sum_s in[s] x_s (in null: all ones); with alpha the sum goes through
+// tanh(alpha u) * w + b on its way out.
+constexpr int MAX_STREAMS = 16;
+
+template <typename TO>
+__global__ void stream_read_kernel(const float* __restrict__ X, int S, const float* __restrict__ in_w, const float* __restrict__ alpha,
+                                   const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ out, int H, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const size_t t = idx / H;
+    const int i = (int)(idx - t * H);
+    const float* src = X + t * S * H + i;
+    float u = 0.0f;
+    for (int s = 0; s < S; s++) u = fmaf(in_w ? in_w[s] : 1.0f, src[(size_t)s * H], u);
+    if (alpha) u = fmaf(tanhf(alpha[0] * u), w[i], b ? b[i] : 0.0f);
+    out[idx] = from_float<TO>(u);
+}
+
+// x_r <- sum_s mix[s, r] x_s + multiplier * out_w[r] * scale[i] * y  for every copy r, from the old copies (mix null: the
+// identity; out_w null: ones; scale null: ones).  A thread owns one (token, column) of all copies.
+__global__ void stream_write_kernel(float* __restrict__ X, int S, const float* __restrict__ mix, const float* __restrict__ out_w,
+                                    const float* __restrict__ scale, float multiplier, const float* __restrict__ y, int H, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const size_t t = idx / H;
+    const int i = (int)(idx - t * H);
+    float* col = X + t * S * H + i;
+    const float add = multiplier * (scale ? scale[i] : 1.0f) * y[idx];
+    float old[MAX_STREAMS];
+#pragma unroll
+    for (int s = 0; s < MAX_STREAMS; s++)
+        if (s < S) old[s] = col[(size_t)s * H];
+#pragma unroll
+    for (int r = 0; r < MAX_STREAMS; r++) {
+        if (r >= S) break;
+        float v;
+        if (mix) {
+            v = 0.0f;
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; s++)
+                if (s < S) v = fmaf(mix[s * S + r], old[s], v);
+        } else {
+            v = old[r];
+        }
+        col[(size_t)r * H] = fmaf(out_w ? out_w[r] : 1.0f, add, v);
+    }
+}
+
+__global__ void stream_spread_kernel(const float* __restrict__ x, float* __restrict__ X, int S, int H, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const size_t t = idx / H;
+    const int i = (int)(idx - t * H);
+    const float v = x[idx];
+    for (int s = 0; s < S; s++) X[(t * S + s) * H + i] = v;
+}
+
+__global__ void stream_sum_kernel(const float* __restrict__ X, const int* __restrict__ rows, int S, float* __restrict__ out, int H,
+                                  size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const size_t r = idx / H;
+    const int i = (int)(idx - r * H);
+    const float* src = X + (size_t)(rows ? rows[r] : r) * S * H + i;
+    float v = 0.0f;
+    for (int s = 0; s < S; s++) v += src[(size_t)s * H];
+    out[idx] = v;
+}
+
+// logits <- cap * tanh(scale * logits / cap)  (cap 0: scale * logits)
+__global__ void logit_finish_kernel(float* __restrict__ logits, float scale, float cap, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float v = logits[idx] * scale;
+    logits[idx] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+
 }  // namespace ember
 
 using namespace ember;
@@ -196,4 +305,63 @@ EMBER_API int ember_round_rows(const float* x, void* out, long long n, void* str
     if (n <= 0) return 0;
     launch_kernel(round_rows_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, (__nv_bfloat16*)out, (size_t)n);
     return check_launch("round_rows");
+}
+
+EMBER_API int ember_dynamic_tanh(const float* x, const int* rows, const float* alpha, const float* w, const float* b, void* out,
+                                 int out_dtype, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || !alpha || !w) return fail("dynamic_tanh: rows of %d need alpha and a weight", H);
+    const size_t n = (size_t)n_rows * H;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == EMBER_F32) launch_kernel(dynamic_tanh_kernel<float>, blocks, 256, 0, st, x, rows, alpha, w, b, (float*)out, H, n);
+    else if (out_dtype == EMBER_BF16)
+        launch_kernel(dynamic_tanh_kernel<__nv_bfloat16>, blocks, 256, 0, st, x, rows, alpha, w, b, (__nv_bfloat16*)out, H, n);
+    else return fail("dynamic_tanh: unsupported output dtype %d", out_dtype);
+    return check_launch("dynamic_tanh");
+}
+
+EMBER_API int ember_stream_read(const float* X, int S, const float* in_w, const float* alpha, const float* w, const float* b, void* out,
+                                int out_dtype, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    if (S <= 0 || S > MAX_STREAMS || H <= 0 || (alpha && !w)) return fail("stream_read: %d copies (at most %d) of rows of %d", S, MAX_STREAMS, H);
+    const size_t n = (size_t)T * H;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == EMBER_F32) launch_kernel(stream_read_kernel<float>, blocks, 256, 0, st, X, S, in_w, alpha, w, b, (float*)out, H, n);
+    else if (out_dtype == EMBER_BF16)
+        launch_kernel(stream_read_kernel<__nv_bfloat16>, blocks, 256, 0, st, X, S, in_w, alpha, w, b, (__nv_bfloat16*)out, H, n);
+    else return fail("stream_read: unsupported output dtype %d", out_dtype);
+    return check_launch("stream_read");
+}
+
+EMBER_API int ember_stream_write(float* X, int S, const float* mix, const float* out_w, const float* scale, float multiplier,
+                                 const float* y, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    if (S <= 0 || S > MAX_STREAMS || H <= 0) return fail("stream_write: %d copies (at most %d) of rows of %d", S, MAX_STREAMS, H);
+    const size_t n = (size_t)T * H;
+    launch_kernel(stream_write_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, X, S, mix, out_w, scale, multiplier, y, H, n);
+    return check_launch("stream_write");
+}
+
+EMBER_API int ember_stream_spread(const float* x, float* X, int S, int T, int H, void* stream) {
+    if (T <= 0) return 0;
+    if (S <= 0 || H <= 0) return fail("stream_spread: %d copies of rows of %d", S, H);
+    const size_t n = (size_t)T * H;
+    launch_kernel(stream_spread_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, x, X, S, H, n);
+    return check_launch("stream_spread");
+}
+
+EMBER_API int ember_stream_sum(const float* X, const int* rows, int S, float* out, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (S <= 0 || H <= 0) return fail("stream_sum: %d copies of rows of %d", S, H);
+    const size_t n = (size_t)n_rows * H;
+    launch_kernel(stream_sum_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, X, rows, S, out, H, n);
+    return check_launch("stream_sum");
+}
+
+EMBER_API int ember_logit_finish(float* logits, float scale, float cap, long long n, void* stream) {
+    if (n <= 0) return 0;
+    launch_kernel(logit_finish_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, logits, scale, cap, (size_t)n);
+    return check_launch("logit_finish");
 }

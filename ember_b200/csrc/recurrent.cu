@@ -1,6 +1,8 @@
-// Recurrent mixers over a ragged batch: a short causal convolution whose last inputs are carried per request, and
-// four matrix-state recurrences (delta rule with a decay per key channel, matrix memory with exponential gating,
-// selective state space with a scalar decay per head, gated linear attention with a decay per key channel).  Everything that enters a recurrence is fp32: decays and
+// Recurrent mixers over a ragged batch: a short causal convolution whose last inputs are carried per request, a blend
+// of every token's input with the previous token's (carried likewise), and
+// five matrix-state recurrences (delta rule with a decay per key channel, matrix memory with exponential gating,
+// selective state space with a scalar decay per head, gated linear attention with a decay per key channel, time mixing
+// that reads the state before it is updated and reaches the current token through a bonus).  Everything that enters a recurrence is fp32: decays and
 // their logarithms, softplus and exponentials, gates, unit norms, the state itself.
 //
 // A step's tokens are S runs (query_start [S + 1]); run s belongs to state slot slots[s].  A recurrence kernel runs
@@ -52,6 +54,37 @@ __global__ void conv_carry_kernel(const float* __restrict__ x, int ldx, int c0, 
         const int src = end - (n - 1) + j;
         cs[(size_t)j * C + c] = src >= first ? x[(size_t)src * ldx + c0 + c] : cs[(size_t)(n - 1 + src - first) * C + c];
     }
+}
+
+// ------------------------------------------------------------------------------- blends with the previous token
+// out[m][t, c] = x[t, c] + (x'[t, c] - x[t, c]) * mu[m, c] for m < n_mix, x' the row of the token before t in its
+// request: the row above inside a run, the request's carried row (zeros for a new request) at the start of a run.
+template <typename TI, typename TO>
+__global__ void token_shift_kernel(const TI* __restrict__ x, int C, const float* __restrict__ mu, int n_mix,
+                                   const float* __restrict__ carry, long long carry_stride, const int* __restrict__ seq_of,
+                                   const int* __restrict__ query_start, const int* __restrict__ slots, TO* __restrict__ out,
+                                   size_t mix_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int s = seq_of[t];
+    const float cur = to_float(x[(size_t)t * C + c]);
+    const float before = t > query_start[s] ? to_float(x[(size_t)(t - 1) * C + c]) : carry[(size_t)slots[s] * carry_stride + c];
+    const float d = before - cur;
+    for (int m = 0; m < n_mix; m++) out[m * mix_stride + (size_t)t * C + c] = from_float<TO>(fmaf(d, mu[(size_t)m * C + c], cur));
+}
+
+// After the blends: every run's last row becomes its request's carried row.
+template <typename TI>
+__global__ void token_carry_kernel(const TI* __restrict__ x, int C, float* __restrict__ carry, long long carry_stride,
+                                   const int* __restrict__ query_start, const int* __restrict__ slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = query_start[s], end = query_start[s + 1];
+    if (end > first) carry[(size_t)slots[s] * carry_stride + c] = to_float(x[(size_t)(end - 1) * C + c]);
 }
 
 // ------------------------------------------------------------------------------------------- state tiles
@@ -197,6 +230,57 @@ __global__ void gla_scan_kernel(GlaArgs p) {
 }
 
 //
+
+// ------------------------------------------------------------------ time mixing, one decay per key channel
+//   o = (S + diag(u) k v^T)^T r;  S <- diag(w) S + k v^T,  w = exp(-exp(z + w0)), u a bonus per head and key channel.
+// The general form (the state tile in shared memory), for more than 256 key channels.
+struct WkvArgs {
+    const float* proj; int ld; int off_r, off_k, off_v;   // [T, ...]: r, k (H D each), v (H V)
+    const float* z; int ld_z;                             // [T, H D] decay logits (before w0)
+    const float* w0; const float* bonus;                  // [H D] each
+    float* state; long long state_stride;                 // [slot][H][D][V]
+    float* out;                                           // [T, H V]
+    const int* query_start; const int* slots;
+    int H, D, V;
+};
+
+__global__ void wkv_scan_kernel(WkvArgs p) {
+    extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, VT = blockDim.x, j = blockIdx.z * VT + threadIdx.x;
+    const int D = p.D, V = p.V;
+    const bool live = j < V;
+    float* tile = smem;                       // [D][VT]
+    float* vec = smem + (size_t)D * VT;       // 2 x (k[D], r[D], w[D], u k[D])
+    float* S = p.state + (size_t)p.slots[s] * p.state_stride + (size_t)h * D * V;
+    load_tile(tile, S, D, V, j, live);
+    const int first = p.query_start[s], end = p.query_start[s + 1];
+    for (int t = first; t < end; t++) {
+        const int b = (t - first) & 1;
+        float* kb = vec + b * 4 * D, *rb = kb + D, *wb = rb + D, *ub = wb + D;
+        const float* row = p.proj + (size_t)t * p.ld;
+        for (int i = threadIdx.x; i < D; i += VT) {
+            const float k = row[p.off_k + h * D + i];
+            kb[i] = k;
+            rb[i] = row[p.off_r + h * D + i];
+            wb[i] = expf(-expf(p.z[(size_t)t * p.ld_z + h * D + i] + p.w0[h * D + i]));
+            ub[i] = p.bonus[h * D + i] * k;
+        }
+        __syncthreads();
+        if (live) {
+            const float v = row[p.off_v + h * V + j];
+            float o = 0.0f;
+            for (int i = 0; i < D; i++) {
+                const float x = tile[i * VT + threadIdx.x];
+                o = fmaf(fmaf(ub[i], v, x), rb[i], o);
+                tile[i * VT + threadIdx.x] = fmaf(kb[i], v, wb[i] * x);
+            }
+            p.out[(size_t)t * p.H * V + h * V + j] = o;
+        }
+    }
+    store_tile(tile, S, D, V, j, live);
+}
 
 // ------------------------------------------------------------- matrix memory with exponential input gate
 // Per head, with log gates i~ = cap tanh((i + b_i) / cap), f~ = logsigmoid(cap tanh((f + b_f) / cap)) and a running
@@ -398,8 +482,10 @@ __device__ __forceinline__ float rows_sum(float v) {
     return v;
 }
 
-// One kernel for the four recurrences (MODE 0 delta rule, 1 matrix memory, 2 state space, 3 gated linear attention:
-// S <- diag(alpha) S + k v^T, o = S^T q with alpha = sigmoid(z + bias)^(1 / tau) per key channel and q times D^-1/2).  A run is walked in chunks
+// One kernel for the five recurrences (MODE 0 delta rule, 1 matrix memory, 2 state space, 3 gated linear attention:
+// S <- diag(alpha) S + k v^T, o = S^T q with alpha = sigmoid(z + bias)^(1 / tau) per key channel and q times D^-1/2; 4 time
+// mixing: o = S^T r + (r . (u k)) v read before S <- diag(w) S + k v^T, w = exp(-exp(z + w0)); the bonus's dot product
+// r . (u k) is a warp sum made with the token's vectors).  A run is walked in chunks
 // of CT tokens: while a chunk is computed from shared memory (no block-wide barrier between its tokens), the next
 // chunk's inputs are already on their way into registers; each warp then prepares its tokens of that chunk (unit
 // norms, decays, gates: a token's vector is spread over the warp's lanes, so its sums are warp sums) and stores
@@ -417,6 +503,7 @@ struct ScanArgs {
     int off_q, off_k, off_v;               // matrix memory: columns of x
     float* gates;                          // matrix memory: [T, H, 4]
     float decay_power;                     // gated linear attention: 1 / tau
+    const float* bonus;                    // time mixing: u [H D] (its w0 is dt_bias)
 };
 
 template <int N>
@@ -431,7 +518,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
     extern __shared__ __align__(16) float smem[];
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int NV = (MODE == 0 || MODE == 3) ? 3 : 2;
+    constexpr int NV = (MODE == 0 || MODE == 3 || MODE == 4) ? 3 : 2;
     constexpr int VS = RG * (RS + 4);               // a vector in shared memory: row group r starts at r (RS + 4)
     constexpr int TOK = NV * VS + 4 + RCOLS;        // vectors, four scalars, the block's 32 column values
     constexpr int TPW = (CT + NW - 1) / NW, EPL = RG * RS / 32;   // (CT: 16 or 8 tokens a chunk for prompt portions, 1 for decode steps)
@@ -449,12 +536,13 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
     float st[RS];
     for (int i = threadIdx.x; i < 2 * CT * TOK; i += RTHREADS) chunks[i] = 0.0f;
     const int first = p.query_start[s], end = p.query_start[s + 1];
-    const float rate = (MODE == 1 || MODE == 3) ? 0.0f : expf(p.A_log[h]);
+    const float rate = (MODE == 1 || MODE == 3 || MODE == 4) ? 0.0f : expf(p.A_log[h]);
     const float qscale = 1.0f / sqrtf((float)D);
     // where this head's vectors start in a row of x
-    const int off0 = MODE == 0 ? p.G * D + grp * D : ((MODE == 1 || MODE == 3) ? p.off_k + h * D : H * V + grp * D);               // k | k | B
-    const int off1 = MODE == 0 ? grp * D : ((MODE == 1 || MODE == 3) ? p.off_q + h * D : H * V + p.G * D + grp * D);               // q | q | C
-    const int off_col = MODE == 0 ? 2 * p.G * D + h * V : ((MODE == 1 || MODE == 3) ? p.off_v + h * V : h * V);                    // v | v | x
+    constexpr bool PROJ = MODE == 1 || MODE == 3 || MODE == 4;        // q (or r), k, v at given columns of one projection
+    const int off0 = MODE == 0 ? p.G * D + grp * D : (PROJ ? p.off_k + h * D : H * V + grp * D);               // k | k | B
+    const int off1 = MODE == 0 ? grp * D : (PROJ ? p.off_q + h * D : H * V + p.G * D + grp * D);               // q | q | C
+    const int off_col = MODE == 0 ? 2 * p.G * D + h * V : (PROJ ? p.off_v + h * V : h * V);                    // v | v | x
 
     float f0[TPW][EPL], f1[TPW][EPL], f2[TPW][EPL], fc[TPW], fs[TPW];
     auto prefetch = [&](int t0) {
@@ -469,7 +557,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                 if (i < D) {
                     f0[w][m] = row[off0 + i];
                     f1[w][m] = row[off1 + i];
-                    if (MODE == 0 || MODE == 3) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
+                    if (MODE == 0 || MODE == 3 || MODE == 4) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
                 }
             }
             const int c = col0 + lane;
@@ -493,6 +581,10 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                     tok[VS + vi] = (MODE == 1 || MODE == 3) ? f1[w][m] * qscale : f1[w][m];
                     if (MODE == 3)      // alpha = sigmoid(z)^(1 / tau) = exp(logsigmoid(z) / tau)
                         tok[2 * VS + vi] = expf(logsigmoidf_(f2[w][m] + (p.dt_bias ? p.dt_bias[h * D + i] : 0.0f)) * p.decay_power);
+                    if (MODE == 4) {
+                        tok[2 * VS + vi] = expf(-expf(f2[w][m] + p.dt_bias[h * D + i]));
+                        s0 = fmaf(f1[w][m] * p.bonus[h * D + i], f0[w][m], s0);          // r . (u k)
+                    }
                     if (MODE == 0) {
                         tok[2 * VS + vi] = expf(-rate * softplusf_(f2[w][m] + p.dt_bias[h * D + i]));
                         s0 = fmaf(f0[w][m], f0[w][m], s0); s1 = fmaf(f1[w][m], f1[w][m], s1); s01 = fmaf(f0[w][m], f1[w][m], s01);
@@ -508,6 +600,9 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                     tok[NV * VS + 2] = s01;                                     // k . q, before the norms
                     tok[NV * VS + 3] = sigmoidf_(fs[w]);
                 }
+            } else if (MODE == 4) {
+                s0 = warp_sum(s0);
+                if (lane == 0) tok[NV * VS + 0] = s0;
             } else if (MODE == 1) {
                 if (lane == 0) {
                     const float* g = p.gates + ((size_t)t * H + h) * 4;
@@ -541,7 +636,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
             for (int i4 = 0; i4 < RS / 4; i4++) {
                 x.v0[i4] = reinterpret_cast<const float4*>(tok + base)[i4];
                 x.v1[i4] = reinterpret_cast<const float4*>(tok + VS + base)[i4];
-                if (MODE == 0 || MODE == 3) x.v2[i4] = reinterpret_cast<const float4*>(tok + 2 * VS + base)[i4];
+                if (MODE == 0 || MODE == 3 || MODE == 4) x.v2[i4] = reinterpret_cast<const float4*>(tok + 2 * VS + base)[i4];
             }
         };
         auto step = [&](int tt, const TokenRegs<RS / 4>& x) {
@@ -571,6 +666,17 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                     st[4 * i4 + 0] = fmaf(k.x, uk, st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, uk, st[4 * i4 + 1]);
                     st[4 * i4 + 2] = fmaf(k.z, uk, st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, uk, st[4 * i4 + 3]);
                 }
+            } else if (MODE == 4) {
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int i4 = 0; i4 < RS / 4; i4++) {
+                    const float4 k = x.v0[i4], q = x.v1[i4], g = x.v2[i4];
+                    acc[0] = fmaf(st[4 * i4 + 0], q.x, acc[0]); acc[1] = fmaf(st[4 * i4 + 1], q.y, acc[1]);
+                    acc[2] = fmaf(st[4 * i4 + 2], q.z, acc[2]); acc[3] = fmaf(st[4 * i4 + 3], q.w, acc[3]);
+                    st[4 * i4 + 0] = fmaf(k.x, x.val, g.x * st[4 * i4 + 0]); st[4 * i4 + 1] = fmaf(k.y, x.val, g.y * st[4 * i4 + 1]);
+                    st[4 * i4 + 2] = fmaf(k.z, x.val, g.z * st[4 * i4 + 2]); st[4 * i4 + 3] = fmaf(k.w, x.val, g.w * st[4 * i4 + 3]);
+                }
+                o = fmaf(x.sc.x, x.val, rows_sum<RG>((acc[0] + acc[1]) + (acc[2] + acc[3])));
             } else if (MODE == 3) {
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -627,7 +733,7 @@ inline bool regs_kernels_on() {
 
 template <int MODE, int RS, int CT, int RG>
 inline int launch_scan_ct(const ScanArgs& p, int S, int n_cols, cudaStream_t st) {
-    constexpr int NV = (MODE == 0 || MODE == 3) ? 3 : 2;
+    constexpr int NV = (MODE == 0 || MODE == 3 || MODE == 4) ? 3 : 2;
     const size_t smem = ((size_t)RG * RS * 33 + 2 * CT * (NV * RG * (RS + 4) + 4 + RCOLS)) * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(scan_chunks_kernel<MODE, RS, CT, RG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -778,4 +884,50 @@ EMBER_API int ember_gla_scan(const float* proj, int ld, int off_q, int off_k, in
     GlaArgs p{proj, ld, off_q, off_k, off_v, z, ld_z, z_bias, decay_power, state, state_stride, out, query_start, slots, H, D, V};
     launch_kernel(gla_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, st, p);
     return check_launch("gla_scan");
+}
+
+EMBER_API int ember_token_shift(const void* x, int x_dtype, const float* mu, int n_mix, float* carry, long long carry_stride,
+                                const int* seq_of, const int* query_start, const int* slots, void* out, int out_dtype,
+                                long long mix_stride, int T, int S, int C, void* stream) {
+    if (T <= 0 || S <= 0) return 0;
+    if (C <= 0 || n_mix <= 0 || mix_stride < (long long)T * C) return fail("token_shift: %d blends of rows of %d, %lld apart", n_mix, C, mix_stride);
+    if (T > 65535 || S > 65535) return fail("token_shift: %d tokens in %d runs are too many for one launch", T, S);
+    if (x_dtype != out_dtype || (x_dtype != EMBER_F32 && x_dtype != EMBER_BF16)) return fail("token_shift: dtypes %d -> %d", x_dtype, out_dtype);
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned bx = (unsigned)((C + 127) / 128);
+    if (x_dtype == EMBER_F32) {
+        launch_kernel(token_shift_kernel<float, float>, dim3(bx, T), 128, 0, st, (const float*)x, C, mu, n_mix, (const float*)carry,
+                      carry_stride, seq_of, query_start, slots, (float*)out, (size_t)mix_stride);
+        launch_kernel(token_carry_kernel<float>, dim3(bx, S), 128, 0, st, (const float*)x, C, carry, carry_stride, query_start, slots);
+    } else {
+        launch_kernel(token_shift_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(bx, T), 128, 0, st, (const __nv_bfloat16*)x, C, mu, n_mix,
+                      (const float*)carry, carry_stride, seq_of, query_start, slots, (__nv_bfloat16*)out, (size_t)mix_stride);
+        launch_kernel(token_carry_kernel<__nv_bfloat16>, dim3(bx, S), 128, 0, st, (const __nv_bfloat16*)x, C, carry, carry_stride,
+                      query_start, slots);
+    }
+    return check_launch("token_shift");
+}
+
+EMBER_API int ember_wkv_scan(const float* proj, int ld, long long off_r, long long off_k, long long off_v, const float* z, int ld_z,
+                             const float* w0, const float* bonus, float* state, long long state_stride, float* out,
+                             const int* query_start, const int* slots, int T, int S, int H, int D, int V, void* stream) {
+    if (S <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || !w0 || !bonus) return fail("wkv_scan: %d heads of %d x %d", H, D, V);
+    if (S > 65535 || H > 65535) return fail("wkv_scan: too many runs or heads for one launch");
+    if (off_r > 0x7fffffffLL || off_k > 0x7fffffffLL || off_v > 0x7fffffffLL) return fail("wkv_scan: column offsets beyond 2^31");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (rows_per_thread(D) && regs_kernels_on()) {
+        ScanArgs q{};
+        q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
+        q.H = H; q.G = H; q.D = D; q.V = V; q.x = proj; q.ld_x = ld; q.off_q = (int)off_r; q.off_k = (int)off_k; q.off_v = (int)off_v;
+        q.a = z; q.ld_a = ld_z; q.dt_bias = w0; q.bonus = bonus;
+        if (launch_scan<4>(q, S, V, T == S, st)) return 1;
+        return check_launch("wkv_scan");
+    }
+    size_t smem;
+    const int VT = pick_columns(D, V, 8 * D, &smem);
+    if (allow_smem(wkv_scan_kernel, smem, "wkv_scan")) return 1;
+    WkvArgs p{proj, ld, (int)off_r, (int)off_k, (int)off_v, z, ld_z, w0, bonus, state, state_stride, out, query_start, slots, H, D, V};
+    launch_kernel(wkv_scan_kernel, dim3(S, H, (V + VT - 1) / VT), VT, smem, st, p);
+    return check_launch("wkv_scan");
 }

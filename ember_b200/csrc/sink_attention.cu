@@ -93,7 +93,8 @@ struct LatentArgs {
     int c_col, kv_rank, rot_dim;       // key/value latent and, behind it, the shared key part to rotate
     const float* q_w; const float* c_w;
     float eps;
-    const float* inv_freq; int rotary; // rotary <= rot_dim elements are rotated in neighbouring pairs
+    const float* inv_freq; int rotary; // rotary <= rot_dim elements are rotated, in neighbouring pairs or (half_layout) i with i + rotary / 2
+    int half_layout; float magnitude;  // cosines and sines are multiplied by magnitude
     const int* positions; const int* seq_of; const int* block_table;
     int max_blocks, page, num_pages;
     void* cq_out;                      // [T, q_rank]
@@ -130,45 +131,46 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(LatentArgs p) {
     T* dst = (T*)p.pool + ((size_t)blk * p.page + pos % p.page) * W;
     for (int i = threadIdx.x; i < p.kv_rank; i += blockDim.x) dst[i] = from_float<T>(row[p.c_col + i] * r * p.c_w[i]);
     const float* kr = row + p.c_col + p.kv_rank;
-    for (int i = threadIdx.x; i < p.rot_dim / 2 + (p.rot_dim & 1); i += blockDim.x) {
-        const int a = 2 * i, c = 2 * i + 1;
-        if (c < p.rotary) {
-            float sn, cs;
-            sincosf((float)pos * p.inv_freq[i], &sn, &cs);
-            const float u = kr[a], v = kr[c];
-            dst[p.kv_rank + a] = from_float<T>(u * cs - v * sn);
-            dst[p.kv_rank + c] = from_float<T>(v * cs + u * sn);
-        } else {
-            dst[p.kv_rank + a] = from_float<T>(kr[a]);
-            if (c < p.rot_dim) dst[p.kv_rank + c] = from_float<T>(kr[c]);
-        }
+    // pair i of the rotation: elements (2i, 2i + 1), or (i, i + rotary / 2) in the half layout
+    for (int i = threadIdx.x; i < p.rotary / 2; i += blockDim.x) {
+        const int a = p.half_layout ? i : 2 * i, c = p.half_layout ? i + p.rotary / 2 : 2 * i + 1;
+        float sn, cs;
+        sincosf((float)pos * p.inv_freq[i], &sn, &cs);
+        sn *= p.magnitude; cs *= p.magnitude;
+        const float u = kr[a], v = kr[c];
+        dst[p.kv_rank + a] = from_float<T>(u * cs - v * sn);
+        dst[p.kv_rank + c] = from_float<T>(v * cs + u * sn);
     }
+    for (int i = p.rotary + threadIdx.x; i < p.rot_dim; i += blockDim.x) dst[p.kv_rank + i] = from_float<T>(kr[i]);
 }
 
-// out[t, h, out_col + i] = rotated in[t, h, in_col + i], i < width; pairs (2i, 2i + 1) below `rotary` turn.
+// out[t, h, out_col + i] = rotated in[t, h, in_col + i], i < width; below `rotary`, pairs (2i, 2i + 1) or, in the half
+// layout, (i, i + rotary / 2) turn by float(position) * inv_freq[i], cosine and sine times `magnitude`.
 template <typename T>
 __global__ void rotate_pairs_kernel(const float* __restrict__ in, int ld_in, int in_head, int in_col, T* __restrict__ out,
                                     int ld_out, int out_head, int out_col, int H, int width, int rotary,
-                                    const float* __restrict__ inv_freq, const int* __restrict__ positions) {
+                                    const float* __restrict__ inv_freq, const int* __restrict__ positions, int half_layout,
+                                    float magnitude) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int half = (width + 1) / 2;
+    const int pairs = rotary / 2, units = pairs + (width - rotary);       // a unit: one pair, or one element that passes
     const float pos = (float)positions[t];
-    for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
+    for (int idx = threadIdx.x; idx < H * units; idx += blockDim.x) {
+        const int h = idx / units, i = idx - h * units;
         const float* src = in + (size_t)t * ld_in + (size_t)h * in_head + in_col;
         T* dst = out + (size_t)t * ld_out + (size_t)h * out_head + out_col;
-        const int a = 2 * i, c = 2 * i + 1;
-        if (c < rotary) {
+        if (i < pairs) {
+            const int a = half_layout ? i : 2 * i, c = half_layout ? i + pairs : 2 * i + 1;
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
+            sn *= magnitude; cs *= magnitude;
             const float u = src[a], v = src[c];
             dst[a] = from_float<T>(u * cs - v * sn);
             dst[c] = from_float<T>(v * cs + u * sn);
         } else {
-            dst[a] = from_float<T>(src[a]);
-            if (c < width) dst[c] = from_float<T>(src[c]);
+            const int e = rotary + (i - pairs);
+            dst[e] = from_float<T>(src[e]);
         }
     }
 }
@@ -900,13 +902,14 @@ EMBER_API int ember_whole_norm_store(const float* qkv, int ld, const float* bias
 EMBER_API int ember_latent_prepare(const float* a, int ld, int q_col, int q_rank, int c_col, int kv_rank, int rot_dim,
                                    const float* q_w, const float* c_w, float eps, const float* inv_freq, int rotary, int T,
                                    const int* positions, const int* seq_of, const int* block_table, int max_blocks, int page,
-                                   int num_pages, void* cq_out, void* pool, int dtype, int write_kv, int* err, void* stream) {
+                                   int num_pages, void* cq_out, void* pool, int dtype, int write_kv, int half_layout, float magnitude,
+                                   int* err, void* stream) {
     if (T <= 0) return 0;
     if (q_rank < 0 || kv_rank <= 0 || rot_dim < 0 || rotary < 0 || rotary > rot_dim || (rotary & 1))
         return fail("latent_prepare: ranks %d / %d, rotated part %d of %d", q_rank, kv_rank, rotary, rot_dim);
     if (write_kv && (page <= 0 || max_blocks <= 0 || num_pages <= 0)) return fail("latent_prepare: bad cache geometry");
     if (rotary > 0 && !inv_freq) return fail("latent_prepare: a rotation needs its frequencies");
-    LatentArgs p{a, ld, q_col, q_rank, c_col, kv_rank, rot_dim, q_w, c_w, eps, inv_freq, rotary, positions, seq_of, block_table,
+    LatentArgs p{a, ld, q_col, q_rank, c_col, kv_rank, rot_dim, q_w, c_w, eps, inv_freq, rotary, half_layout, magnitude, positions, seq_of, block_table,
                  max_blocks, page, num_pages, cq_out, pool, write_kv, err};
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == EMBER_F32) launch_kernel(latent_prepare_kernel<float>, T, 256, 0, st, p);
@@ -917,16 +920,16 @@ EMBER_API int ember_latent_prepare(const float* a, int ld, int q_col, int q_rank
 
 EMBER_API int ember_rotate_pairs(const float* in, int ld_in, int in_head, int in_col, void* out, int ld_out, int out_head,
                                  int out_col, int dtype, int T, int H, int width, int rotary, const float* inv_freq,
-                                 const int* positions, void* stream) {
+                                 const int* positions, int half_layout, float magnitude, void* stream) {
     if (T <= 0 || width <= 0) return 0;
     if (rotary < 0 || rotary > width || (rotary & 1) || (rotary > 0 && !inv_freq)) return fail("rotate_pairs: %d of %d rotated", rotary, width);
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == EMBER_F32)
         launch_kernel(rotate_pairs_kernel<float>, T, 128, 0, st, in, ld_in, in_head, in_col, (float*)out, ld_out, out_head, out_col, H,
-                      width, rotary, inv_freq, positions);
+                      width, rotary, inv_freq, positions, half_layout, magnitude);
     else if (dtype == EMBER_BF16)
         launch_kernel(rotate_pairs_kernel<__nv_bfloat16>, T, 128, 0, st, in, ld_in, in_head, in_col, (__nv_bfloat16*)out, ld_out,
-                      out_head, out_col, H, width, rotary, inv_freq, positions);
+                      out_head, out_col, H, width, rotary, inv_freq, positions, half_layout, magnitude);
     else return fail("rotate_pairs: unsupported dtype %d", dtype);
     return check_launch("rotate_pairs");
 }

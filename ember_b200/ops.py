@@ -18,7 +18,9 @@ F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
 EPI_SUMS = 5      # tensor-core product of at most 128 tokens: the fp32 sums stay in the split-K scratch
 EPI_RELU_MUL = 6  # the gated epilogue with relu: relu(c[2j]) * c[2j + 1]
-GATED_EPILOGUES = (EPI_SILU_MUL, EPI_RELU_MUL)
+EPI_GELU_MUL = 7  # ... with the tanh form of gelu: 0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * c[2j + 1]
+GATED_EPILOGUES = (EPI_SILU_MUL, EPI_RELU_MUL, EPI_GELU_MUL)
+GATED_EPILOGUE_OF = {"silu": EPI_SILU_MUL, "relu": EPI_RELU_MUL, "gelu_tanh": EPI_GELU_MUL}
 
 
 class KernelError(RuntimeError):
@@ -659,7 +661,103 @@ def scaled_sum(x: torch.Tensor, a: float, y: Optional[torch.Tensor], b: float, o
           _stream(stream))
 
 
-ACTIVATIONS = ("silu", "relu")      # what the gated epilogue of the products takes (EPI_SILU_MUL, EPI_RELU_MUL)
+def dynamic_tanh(x: torch.Tensor, alpha: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                 n_rows: int, rows: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out[r] = tanh(alpha * x[rows[r] or r]) * weight + bias, element by element; x fp32, ``alpha`` a device scalar."""
+    for t, n in ((x, "x"), (alpha, "alpha"), (weight, "weight")) + (((bias, "bias"),) if bias is not None else ()):
+        _check(t, n, torch.float32)
+    _check(out, "out")
+    H = x.shape[-1]
+    if weight.numel() != H or alpha.numel() != 1 or out.shape[-1] != H or out.numel() < n_rows * H or (bias is not None and bias.numel() != H):
+        raise KernelError(f"dynamic_tanh: width {H}, weight {tuple(weight.shape)}, out {tuple(out.shape)} for {n_rows} rows")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_dynamic_tanh, _p(x), _p(rows), _p(alpha), _p(weight), _p(bias), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(H), _stream(stream))
+
+
+STREAMS_MAX = 16                 # copies of the residual stream the stream kernels take (their MAX_STREAMS)
+
+
+def stream_read(X: torch.Tensor, streams: int, in_w: Optional[torch.Tensor], out: torch.Tensor, T: int,
+                norm=None, stream: Optional[int] = None) -> None:
+    """out[t] = sum_s in_w[s] * X[t, s] over the ``streams`` copies of the residual stream (X fp32 [T, streams width];
+    ``in_w`` None: ones).  ``norm`` = (alpha, weight, bias): the sum goes through tanh(alpha u) * weight + bias."""
+    _check(X, "X", torch.float32)
+    _check(out, "out")
+    H = out.shape[-1]
+    if X.shape[-1] != streams * H or X.numel() < T * streams * H or out.numel() < T * H:
+        raise KernelError(f"stream_read: {streams} copies of width {H} in rows of {X.shape[-1]}")
+    if in_w is not None:
+        _check(in_w, "in_w", torch.float32)
+        if in_w.numel() != streams:
+            raise KernelError("stream_read: one weight per copy")
+    alpha, w, b = norm if norm is not None else (None, None, None)
+    for t, n in ((alpha, "alpha"), (w, "weight"), (b, "bias")):
+        if t is not None:
+            _check(t, n, torch.float32)
+    if norm is None and out.dtype != torch.float32:
+        raise KernelError("stream_read: the plain sum is fp32")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_stream_read, _p(X), c_int(streams), _p(in_w), _p(alpha), _p(w), _p(b), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(T), c_int(H), _stream(stream))
+
+
+def stream_write(X: torch.Tensor, streams: int, mix: Optional[torch.Tensor], out_w: Optional[torch.Tensor],
+                 scale: Optional[torch.Tensor], multiplier: float, y: torch.Tensor, T: int, stream: Optional[int] = None) -> None:
+    """Every copy r at once from the old copies: X[t, r] <- sum_s mix[s, r] X[t, s] + multiplier * out_w[r] * scale * y[t]
+    (``mix`` fp32 [streams, streams] or None: the identity; ``out_w`` None: ones; ``scale`` fp32 [width] or None)."""
+    _check(X, "X", torch.float32)
+    _check(y, "y", torch.float32)
+    H = y.shape[-1]
+    if X.shape[-1] != streams * H or X.numel() < T * streams * H or y.numel() < T * H:
+        raise KernelError(f"stream_write: {streams} copies of width {H} in rows of {X.shape[-1]}")
+    for t, n, size in ((mix, "mix", streams * streams), (out_w, "out_w", streams), (scale, "scale", H)):
+        if t is not None:
+            _check(t, n, torch.float32)
+            if t.numel() != size:
+                raise KernelError(f"stream_write: {n} has {t.numel()} elements, not {size}")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_stream_write, _p(X), c_int(streams), _p(mix), _p(out_w), _p(scale), c_float(multiplier), _p(y), c_int(T),
+          c_int(H), _stream(stream))
+
+
+def stream_spread(x: torch.Tensor, X: torch.Tensor, streams: int, T: int, stream: Optional[int] = None) -> None:
+    """X[t, s] = x[t] for every copy s (fp32)."""
+    _check(x, "x", torch.float32)
+    _check(X, "X", torch.float32)
+    H = x.shape[-1]
+    if X.shape[-1] != streams * H or X.numel() < T * streams * H or x.numel() < T * H:
+        raise KernelError("stream_spread: buffers do not fit")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_stream_spread, _p(x), _p(X), c_int(streams), c_int(T), c_int(H), _stream(stream))
+
+
+def stream_sum(X: torch.Tensor, streams: int, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None,
+               stream: Optional[int] = None) -> None:
+    """out[r] = sum over the copies of X[rows[r] or r] (fp32)."""
+    _check(X, "X", torch.float32)
+    _check(out, "out", torch.float32)
+    H = out.shape[-1]
+    if X.shape[-1] != streams * H or out.numel() < n_rows * H:
+        raise KernelError("stream_sum: buffers do not fit")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_stream_sum, _p(X), _p(rows), c_int(streams), _p(out), c_int(n_rows), c_int(H), _stream(stream))
+
+
+def logit_finish(logits: torch.Tensor, n: int, scale: float, cap: float, stream: Optional[int] = None) -> None:
+    """logits[:n] <- cap * tanh(scale * logits / cap) in place (cap 0: scale * logits); fp32."""
+    _check(logits, "logits", torch.float32)
+    if logits.numel() < n:
+        raise KernelError("logit_finish: the buffer is too small")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_logit_finish, _p(logits), c_float(scale), c_float(cap), c_longlong(n), _stream(stream))
+
+
+ACTIVATIONS = tuple(GATED_EPILOGUE_OF)      # what the gated epilogue of the products takes
 
 
 # -------------------------------------------------------------------- recurrent mixers (csrc/recurrent.cu)
@@ -745,6 +843,51 @@ def ssm_scan(conv: torch.Tensor, dt: torch.Tensor, dt_col: int, dt_bias: torch.T
     _call(lib, lib.ember_ssm_scan, _p(conv), c_int(conv.shape[1]), _off(dt, dt_col), c_int(dt.shape[1]), _p(dt_bias), _p(A_log),
           _p(skip), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(T), c_int(S), c_int(heads),
           c_int(groups), c_int(n_state), c_int(vdim), _stream(stream))
+
+
+def token_shift(x: torch.Tensor, mu: torch.Tensor, carry: torch.Tensor, carry_col: int, seq_of: torch.Tensor,
+                query_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, T: int, S: int,
+                stream: Optional[int] = None) -> None:
+    """out[m, t] = x[t] + (x'[t] - x[t]) * mu[m] for every blend m (``mu`` fp32 [blends, width]), x' the row of the token
+    before t in its request: the row above inside a run, else the request's carried row (columns carry_col .. + width of
+    its row of ``carry`` fp32 [slots, row]; zeros for a new request).  The carried rows are then replaced by the runs'
+    last rows.  ``out`` [blends, rows, width] has x's dtype."""
+    _check(x, "x")
+    _check(out, "out", x.dtype)
+    _check(mu, "mu", torch.float32)
+    _check(carry, "carry", torch.float32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check_runs(query_start, slots, S)
+    n_mix, C = mu.shape
+    if x.shape[-1] != C or x.numel() < T * C or out.dim() != 3 or out.shape[0] != n_mix or out.shape[2] != C or out.shape[1] < T or \
+            carry.dim() != 2 or carry_col + C > carry.shape[1]:
+        raise KernelError(f"token_shift: {n_mix} blends of width {C}: x {tuple(x.shape)}, out {tuple(out.shape)}, carry {tuple(carry.shape)}")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_token_shift, _p(x), c_int(dtype_code(x.dtype)), _p(mu), c_int(n_mix), _off(carry, carry_col),
+          c_longlong(carry.shape[1]), _p(seq_of), _p(query_start), _p(slots), _p(out), c_int(dtype_code(out.dtype)),
+          c_longlong(out.shape[1] * C), c_int(T), c_int(S), c_int(C), _stream(stream))
+
+
+def wkv_scan(proj: torch.Tensor, ld: int, off_r: int, off_k: int, off_v: int, z: torch.Tensor, z_col: int, w0: torch.Tensor,
+             bonus: torch.Tensor, state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
+             T: int, S: int, heads: int, dim: int, vdim: int, stream: Optional[int] = None) -> None:
+    """Time mixing over the step's runs: per head o = (S + diag(u) k v^T)^T r, then S <- diag(w) S + k v^T with
+    w = exp(-exp(z + w0)) per key channel.  ``proj`` fp32 holds r, k, v in rows of ``ld`` elements starting ``off_*``
+    elements behind its first (they may be separate blocks of one buffer); ``z`` fp32 rows hold the decay logits
+    [heads dim] from column z_col; ``w0``, ``bonus`` fp32 [heads dim]; the state [slots, >= heads dim vdim] fp32 is read
+    and left updated; out fp32 [T, heads vdim]."""
+    for t, n in ((proj, "proj"), (z, "z"), (w0, "w0"), (bonus, "bonus"), (state, "state"), (out, "out")):
+        _check(t, n, torch.float32)
+    _check_runs(query_start, slots, S)
+    last = (T - 1) * ld
+    if max(off_r, off_k) + last + heads * dim > proj.numel() or off_v + last + heads * vdim > proj.numel() or \
+            z_col + heads * dim > z.shape[1] or state.dim() != 2 or state.shape[1] < heads * dim * vdim or \
+            out.numel() < T * heads * vdim or w0.numel() != heads * dim or bonus.numel() != heads * dim:
+        raise KernelError("wkv_scan: buffers do not fit the head geometry")
+    lib = _lib("recurrent")
+    _call(lib, lib.ember_wkv_scan, _p(proj), c_int(ld), c_longlong(off_r), c_longlong(off_k), c_longlong(off_v), _off(z, z_col),
+          c_int(z.shape[1]), _p(w0), _p(bonus), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots), c_int(T),
+          c_int(S), c_int(heads), c_int(dim), c_int(vdim), _stream(stream))
 
 
 # ------------------------------------------------------- attention without softmax (csrc/sigmoid_attention.cu)
@@ -873,14 +1016,19 @@ def whole_norm_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optio
 
 def latent_prepare(a: torch.Tensor, q_col: int, q_rank: int, c_col: int, kv_rank: int, rot_dim: int, q_w: Optional[torch.Tensor],
                    c_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rotary: int, T: int,
-                   positions: torch.Tensor, seq_of: torch.Tensor, block_table: torch.Tensor, page: int, cq_out: torch.Tensor,
+                   positions: torch.Tensor, seq_of: torch.Tensor, block_table: torch.Tensor, page: int, cq_out: Optional[torch.Tensor],
                    pool: Optional[torch.Tensor], write_kv: bool = True, err: Optional[torch.Tensor] = None,
-                   stream: Optional[int] = None) -> None:
+                   stream: Optional[int] = None, half_layout: bool = False, magnitude: float = 1.0) -> None:
     """From the fused down-projections ``a`` fp32 [T, ld]: the query latent (columns q_col.., RMS norm with ``q_w``) to
-    ``cq_out`` [T, q_rank]; with ``write_kv`` the key/value latent (columns c_col.., RMS norm with ``c_w``) and behind it
-    the shared key part (rot_dim columns, the first ``rotary`` rotated in neighbouring pairs) into the token's cache
+    ``cq_out`` [T, q_rank] (none with q_rank 0); with ``write_kv`` the key/value latent (columns c_col.., RMS norm with
+    ``c_w``) and behind it the shared key part (rot_dim columns, the first ``rotary`` rotated: neighbouring pairs, or
+    element i with i + rotary / 2 under ``half_layout``; cosines and sines times ``magnitude``) into the token's cache
     row [kv_rank + rot_dim] of ``pool`` [pages, 1, page, kv_rank + rot_dim]."""
     _check(a, "a", torch.float32)
+    if cq_out is None:
+        if q_rank or pool is None:
+            raise KernelError("latent_prepare: no output for the query latent")
+        cq_out = pool                   # (only its type is read)
     _check(cq_out, "cq_out")
     for t, n in ((positions, "positions"), (seq_of, "seq_of"), (block_table, "block_table")):
         _check(t, n, torch.int32)
@@ -900,14 +1048,16 @@ def latent_prepare(a: torch.Tensor, q_col: int, q_rank: int, c_col: int, kv_rank
     _call(lib, lib.ember_latent_prepare, _p(a), c_int(a.shape[1]), c_int(q_col), c_int(q_rank), c_int(c_col), c_int(kv_rank),
           c_int(rot_dim), _p(q_w), _p(c_w), c_float(eps), _p(inv_freq), c_int(rotary if write_kv else 0), c_int(T), _p(positions),
           _p(seq_of), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(pool.shape[0] if pool is not None else 1),
-          _p(cq_out), _p(pool), c_int(dtype_code(cq_out.dtype)), c_int(1 if write_kv else 0), _p(err), _stream(stream))
+          _p(cq_out), _p(pool), c_int(dtype_code(cq_out.dtype)), c_int(1 if write_kv else 0), c_int(1 if half_layout else 0),
+          c_float(magnitude), _p(err), _stream(stream))
 
 
 def rotate_pairs(x: torch.Tensor, x_head: int, x_col: int, out: torch.Tensor, out_head: int, out_col: int, T: int, heads: int,
                  width: int, rotary: int, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
-                 stream: Optional[int] = None) -> None:
-    """out[t, h, out_col + i] = x[t, h, x_col + i] for i < width, with pairs (2i, 2i + 1) below ``rotary`` turned by
-    float(position) * inv_freq[i]; x fp32 rows of heads ``x_head`` apart, out rows of heads ``out_head`` apart."""
+                 stream: Optional[int] = None, half_layout: bool = False, magnitude: float = 1.0) -> None:
+    """out[t, h, out_col + i] = x[t, h, x_col + i] for i < width, with pairs (2i, 2i + 1) (under ``half_layout``:
+    (i, i + rotary / 2)) below ``rotary`` turned by float(position) * inv_freq[i], cosine and sine times ``magnitude``;
+    x fp32 rows of heads ``x_head`` apart, out rows of heads ``out_head`` apart."""
     _check(x, "x", torch.float32)
     _check(out, "out")
     _check(positions, "positions", torch.int32)
@@ -921,7 +1071,7 @@ def rotate_pairs(x: torch.Tensor, x_head: int, x_col: int, out: torch.Tensor, ou
     lib = _lib("sink_attention")
     _call(lib, lib.ember_rotate_pairs, _p(x), c_int(x.shape[1]), c_int(x_head), c_int(x_col), _p(out), c_int(out.shape[1]),
           c_int(out_head), c_int(out_col), c_int(dtype_code(out.dtype)), c_int(T), c_int(heads), c_int(width), c_int(rotary),
-          _p(inv_freq), _p(positions), _stream(stream))
+          _p(inv_freq), _p(positions), c_int(1 if half_layout else 0), c_float(magnitude), _stream(stream))
 
 
 def head_gemm(x: torch.Tensor, x_head: int, x_col: int, w: torch.Tensor, out: torch.Tensor, out_head: int, out_col: int, T: int,
@@ -998,16 +1148,33 @@ def moe_stream_usable(x: torch.Tensor, K: int) -> bool:
     return (K * x.element_size()) % 16 == 0 and MOE_STREAM_ROWS * K * x.element_size() <= 200 * 1024
 
 
-def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor, stream: Optional[int] = None) -> None:
+def _route_rule(rule, experts: int):
+    """(sigmoid, correction pointer, scale, renormalize) of a routing rule: None is the softmax over the chosen logits;
+    else (correction fp32 [experts] or None, scale, renormalize) for sigmoid scores."""
+    if rule is None:
+        return c_int(0), c_void_p(0), c_float(1.0), c_int(0)
+    correction, scale, renormalize = rule
+    if correction is not None:
+        _check(correction, "correction", torch.float32)
+        if correction.numel() != experts:
+            raise KernelError(f"routing: a correction of {correction.numel()} for {experts} experts")
+    return c_int(1), _p(correction), c_float(scale), c_int(1 if renormalize else 0)
+
+
+def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor, stream: Optional[int] = None,
+              rule=None) -> None:
     """sel[t] = the ``top`` experts with the largest logits (descending; ties: the lower index), wgt[t] = softmax over
-    those logits alone.  logits fp32 [T, experts]."""
+    those logits alone.  logits fp32 [T, experts].  With ``rule`` = (correction, scale, renormalize): scores are
+    sigmoid(logits), the choice is by score + correction, the weights are the chosen scores times scale (divided by
+    their sum first if renormalize)."""
     _check(logits, "logits", torch.float32)
     _check(sel, "sel", torch.int32)
     _check(wgt, "wgt", torch.float32)
     if logits.dim() != 2 or logits.shape[0] < T or sel.numel() < T * top or wgt.numel() < T * top:
         raise KernelError("moe_route: buffers do not fit the step")
     lib = _lib("moe")
-    _call(lib, lib.ember_moe_route, _p(logits), c_int(T), c_int(logits.shape[1]), c_int(top), _p(sel), _p(wgt), _stream(stream))
+    _call(lib, lib.ember_moe_route, _p(logits), c_int(T), c_int(logits.shape[1]), c_int(top), _p(sel), _p(wgt),
+          *_route_rule(rule, logits.shape[1]), _stream(stream))
 
 
 def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
@@ -1029,11 +1196,11 @@ def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tens
 
 def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
              tiles: torch.Tensor, max_tiles: int, top: int, gated: bool, limit: float = 0.0, alpha: float = 1.0,
-             stream: Optional[int] = None, streaming: bool = False) -> None:
+             stream: Optional[int] = None, streaming: bool = False, up_offset: float = 1.0) -> None:
     """The product of every slot's row with its expert's matrix (``w`` [experts, N, K]).  ``top`` > 0: a slot's row of
     ``x`` is its token's (x [tokens, K], gathered through the pairs); 0: x has a row per slot.  ``gated``: w's rows are
-    interleaved (gate, up) and out[slot, j] = g sigmoid(alpha g) (u + 1) with g = min(gate, limit),
-    u = clamp(up, -limit, limit), in x's dtype; else out[slot] is the fp32 product.  ``streaming``: the form for tile
+    interleaved (gate, up) and out[slot, j] = g sigmoid(alpha g) (u + up_offset) with g = min(gate, limit),
+    u = clamp(up, -limit, limit) (``limit`` may be infinite), in x's dtype; else out[slot] is the fp32 product.  ``streaming``: the form for tile
     lists of 16-row tiles (``moe_group`` with ``MOE_STREAM_ROWS``), else the form for 32-row tiles."""
     _check(x, "x")
     _check(w, "w", x.dtype)
@@ -1046,7 +1213,7 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch
     _call(lib, lib.ember_moe_stream if streaming else lib.ember_moe_gemm, _p(x), c_int(dtype_code(x.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)), c_longlong(N * K),
           _p(out), c_int(dtype_code(out.dtype)), c_int(n_out), _p(offsets), _p(pair_of_slot), _off(tiles, 0), _off(tiles, 1),
           _off(tiles, 1 + max_tiles), c_int(max_tiles), c_int(top), c_int(N), c_int(K), c_int(1 if gated else 0), c_float(limit),
-          c_float(alpha), _stream(stream))
+          c_float(alpha), c_float(up_offset), _stream(stream))
 
 
 def moe_combine(y: torch.Tensor, wgt: torch.Tensor, slot_of_pair: torch.Tensor, T: int, top: int, out: torch.Tensor,
@@ -1076,8 +1243,9 @@ def moe_gather(x: torch.Tensor, pair_of_slot: torch.Tensor, n_pairs: int, top: i
     _call(lib, lib.ember_moe_gather, _p(x), _p(pair_of_slot), c_int(n_pairs), c_int(top), _p(xs), c_int(row), _stream(stream))
 
 
-def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float, alpha: float, stream: Optional[int] = None) -> None:
-    """act[r, j] = g sigmoid(alpha g) (u + 1) with g = min(gu[r, 2j], limit), u = clamp(gu[r, 2j + 1], -limit, limit); gu fp32."""
+def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float, alpha: float, stream: Optional[int] = None,
+                   up_offset: float = 1.0) -> None:
+    """act[r, j] = g sigmoid(alpha g) (u + up_offset) with g = min(gu[r, 2j], limit), u = clamp(gu[r, 2j + 1], -limit, limit); gu fp32."""
     _check(gu, "gu", torch.float32)
     _check(act, "act")
     n = act.shape[-1]
@@ -1085,13 +1253,13 @@ def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float,
         raise KernelError("moe_activation: buffers do not fit")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_activation, _p(gu), _p(act), c_int(dtype_code(act.dtype)), c_longlong(rows * n), c_float(limit),
-          c_float(alpha), _stream(stream))
+          c_float(alpha), c_float(up_offset), _stream(stream))
 
 
 def moe_router(x: torch.Tensor, w: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
-               logits: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
-    """The router's logits x[t] . w[e] (``w`` fp32 [experts, K], fp32 sums) and ``moe_route`` on them in one kernel;
-    ``logits`` (fp32 [T, experts]) receives them if given."""
+               logits: Optional[torch.Tensor] = None, stream: Optional[int] = None, rule=None) -> None:
+    """The router's logits x[t] . w[e] (``w`` fp32 [experts, K], fp32 sums) and ``moe_route`` on them (with its
+    ``rule``) in one kernel; ``logits`` (fp32 [T, experts]) receives them if given."""
     _check(x, "x")
     _check(w, "w", torch.float32)
     _check(sel, "sel", torch.int32)
@@ -1105,7 +1273,7 @@ def moe_router(x: torch.Tensor, w: torch.Tensor, T: int, top: int, sel: torch.Te
             raise KernelError("moe_router: the logits do not fit")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_router, _p(x), c_int(dtype_code(x.dtype)), _p(w), c_int(T), c_int(K), c_int(E), c_int(top), _p(sel),
-          _p(wgt), _p(logits), _stream(stream))
+          _p(wgt), _p(logits), *_route_rule(rule, E), _stream(stream))
 
 
 SHARED_ROW_TC_ROWS = 64          # (query, head) rows of a block of the tensor-core form (its LT_ROWS)

@@ -16,6 +16,8 @@ Interfaces (what a new part must provide):
   it *adds* its result to ``residual``.
 * ``FeedForward``:   ``forward(ctx, x[T, hidden], residual_f32[T, hidden])``; it adds its result.
 * ``Gate``:          ``forward(ctx, x[T, hidden], logits_f32[T, size])``.
+* ``Connection``:    ``read(ctx, streams_f32[T, copies * hidden], norm, out[T, hidden])`` and
+  ``write(ctx, streams_f32, y_f32[T, hidden])``: how a sublayer reads from and writes to the copies of the residual stream.
 * Mixers and feed-forwards with ``can_store = True`` also take ``accumulate=False``: the result is stored, not added.
 
 No part knows which model it is in: sizes and constants come from its spec, weights from the
@@ -177,6 +179,20 @@ class Gate(Part):
 
     def forward(self, ctx, x: torch.Tensor, logits: torch.Tensor) -> None:
         """logits[T, size] (fp32) = what the sigmoid is taken of, less the part's ``bias`` (fp32 [size] or None)."""
+        raise NotImplementedError
+
+
+class Connection(Part):
+    """How one sublayer is joined to the residual stream when the model keeps it in several copies
+    (``ModelSpec.residual_streams``): ``read`` makes the sublayer's normed input from the copies, ``write`` updates every
+    copy from the old ones and the sublayer's fp32 result."""
+
+    family = "connection"
+
+    def read(self, ctx, streams: torch.Tensor, norm, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+    def write(self, ctx, streams: torch.Tensor, y: torch.Tensor) -> None:
         raise NotImplementedError
 
 

@@ -188,5 +188,58 @@ class GatedSandwichBlock(Arrangement):
                            p.get("feed_forward_gate"), p["feed_forward_out_norm"], store)
 
 
+class ConnectedPreNormBlock(Arrangement):
+    """Pre-norm sublayers joined to the residual stream by *connections*:
+
+        x = norm(connection.read(streams));  y = sublayer(x);  connection.write(streams, y)
+
+    once for the mixer and once for the feed-forward (a layer may have none).  The model keeps the stream in
+    ``ModelSpec.residual_streams`` copies, ``h`` is [tokens, copies * hidden]; the connection says how the copies are
+    read and written (hyper-connections, a residual multiplier, layer scale).  The sublayer stores its fp32 result in a
+    buffer (``can_store``; others add into a zeroed one)."""
+
+    ROLES = {"mixer_norm": "norm", "mixer": "mixer", "mixer_connection": "connection",
+             "feed_forward_norm": "norm", "feed_forward": "feed_forward", "feed_forward_connection": "connection"}
+    OPTIONAL = frozenset({"feed_forward_norm", "feed_forward", "feed_forward_connection"})
+
+    def __init__(self, layer_spec):
+        super().__init__(layer_spec)
+        p = self.parts
+        have = [r in p for r in ("feed_forward_norm", "feed_forward", "feed_forward_connection")]
+        if any(have) and not all(have):
+            raise ConfigError("a connected layer has a feed-forward with its norm and its connection, or none of the three")
+        sizes = {(c.spec.streams, c.spec.size) for r, c in p.items() if self.ROLES[r] == "connection"}
+        if len(sizes) != 1:
+            raise ConfigError("the connections of a layer must agree on the copies of the stream and on its width")
+        self.streams, self.hidden = next(iter(sizes))
+
+    def _sublayer(self, ctx, h, norm, run, connection, can_store: bool) -> None:
+        x = ctx.buf("block.normed", (ctx.max_tokens, self.hidden), self.rt.dtype)
+        y = ctx.buf("block.sublayer", (ctx.max_tokens, self.hidden), torch.float32)
+        connection.read(ctx, h, norm, x)
+        if not can_store:
+            y[:ctx.T].zero_()
+        run(x, y)
+        connection.write(ctx, h, y)
+
+    def forward(self, ctx, h: torch.Tensor, caches, owns_cache: bool = True) -> None:
+        p = self.parts
+        if h.shape[-1] != self.streams * self.hidden:
+            raise ConfigError(f"the layer is connected to {self.streams} copies of width {self.hidden}; the model's stream has "
+                              f"rows of {h.shape[-1]}")
+        mixer = p["mixer"]
+        store = bool(getattr(mixer, "can_store", False))
+        kw = {"accumulate": False} if store else {}
+        self._sublayer(ctx, h, p["mixer_norm"], lambda x, y: mixer.forward(ctx, x, y, self.cache_of(caches), owns_cache, **kw),
+                       p["mixer_connection"], store)
+        ff = p.get("feed_forward")
+        if ff is not None:
+            store = bool(getattr(ff, "can_store", False))
+            kw = {"accumulate": False} if store else {}
+            self._sublayer(ctx, h, p["feed_forward_norm"], lambda x, y: ff.forward(ctx, x, y, **kw),
+                           p["feed_forward_connection"], store)
+
+
 register_part("arrangement", "prenorm", PreNormBlock)
+register_part("arrangement", "connected_prenorm", ConnectedPreNormBlock)
 register_part("arrangement", "gated_sandwich", GatedSandwichBlock)

@@ -1,4 +1,4 @@
-"""Gated feed-forward: h += down( act(gate(x)) * up(x) ), no biases; act = silu (SwiGLU) or relu.
+"""Gated feed-forward: h += down( act(gate(x)) * up(x) ), no biases; act = silu (SwiGLU), relu or gelu (tanh form).
 
 Formula: src/backend/cpu/cpu_backend.cpp:204-211 with silu(g) = g / (1 + exp(-g)).
 Device layout: gate and up rows are interleaved (even rows gate, odd rows up) into one
@@ -50,15 +50,18 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, accumulate: bool = True) -> None:
         s = self.spec
         act = ctx.buf("gated_mlp.act", (ctx.max_tokens, s.intermediate_size), self.rt.dtype)
-        self.gate_up(ctx, x, act, ctx.T, ops.EPI_SILU_MUL if s.activation == "silu" else ops.EPI_RELU_MUL)
+        self.gate_up(ctx, x, act, ctx.T, ops.GATED_EPILOGUE_OF[s.activation])
         self.down(ctx, act, residual, ctx.T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 
 class RoutedMLP(FeedForward):
-    """Mixture of experts: h += sum over the token's ``top`` experts of weight * W_down (g sigmoid(alpha g) (u + 1)) with
-    g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit).  The router's logits W_router x are fp32 (fp32 weights
-    and accumulation); the chosen experts are the ``top`` largest (ties: the lower index) and their weights the softmax
-    over the chosen logits alone.
+    """Mixture of experts: h += sum over the token's ``top`` experts of weight * W_down (g sigmoid(alpha g) (u + up_offset))
+    with g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit) (``limit`` 0: no clamps; alpha 1 and up_offset 0 then
+    give silu(W_gate x) * W_up x).  The router's logits W_router x are fp32 (fp32 weights and accumulation).  Scoring
+    "softmax_top": the chosen experts are the ``top`` largest logits (ties: the lower index) and their weights the
+    softmax over the chosen logits alone.  Scoring "sigmoid": scores s = sigmoid(logits), the choice is by
+    s + correction (a stored vector, if ``correction``), the weights are the chosen experts' s times ``route_scale``
+    (divided by their sum first if ``renormalize``).
 
     Device layout: every expert's gate and up rows interleaved into one [experts, 2 ff, hidden] tensor (the activation
     is the first product's epilogue) and the down matrices as [experts, hidden, ff].  The step's (token, choice) pairs
@@ -70,7 +73,7 @@ class RoutedMLP(FeedForward):
     tokens' rows are gathered expert by expert, the host reads the experts' row counts (the step's one look at the
     device) and every expert with rows runs the tcgen05 product on its slice, first gate/up into fp32, an element-wise
     kernel for the clamped activation, then down; the weighted sum over a token's choices is the same kernel either way.
-    Tensors under the prefix: router, e<i>.gate, e<i>.up, e<i>.down."""
+    Tensors under the prefix: router, correction (if any), e<i>.gate, e<i>.up, e<i>.down."""
 
     graph_safe = True
     can_store = True
@@ -84,12 +87,19 @@ class RoutedMLP(FeedForward):
             raise ConfigError(f"routed feed-forward: top {s.top} of {s.experts} experts of {s.intermediate_size}")
         if s.experts > ops.MOE_MAX_EXPERTS or s.top > ops.MOE_MAX_TOP:
             raise ConfigError(f"routed feed-forward: at most {ops.MOE_MAX_TOP} of {ops.MOE_MAX_EXPERTS} experts")
-        if not s.limit > 0:
-            raise ConfigError("routed feed-forward: the clamp limit must be positive")
+        if s.limit < 0:
+            raise ConfigError("routed feed-forward: the clamp limit must be positive (or 0 for none)")
+        if s.scoring not in ("softmax_top", "sigmoid"):
+            raise ConfigError(f"routed feed-forward: scoring {s.scoring!r} (softmax_top, sigmoid)")
+        if s.scoring != "sigmoid" and (s.correction or s.renormalize or s.route_scale != 1.0):
+            raise ConfigError("routed feed-forward: a correction, a scale and renormalising belong to sigmoid scoring")
+        self.limit = float(s.limit) if s.limit > 0 else float("inf")
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
         d = [WeightDecl(p + "router", (s.experts, s.hidden_size))]
+        if s.correction:
+            d.append(WeightDecl(p + "correction", (s.experts,), init="uniform", lo=-0.2, hi=0.2))
         for e in range(s.experts):
             d += [WeightDecl(f"{p}e{e}.gate", (s.intermediate_size, s.hidden_size)),
                   WeightDecl(f"{p}e{e}.up", (s.intermediate_size, s.hidden_size)),
@@ -106,6 +116,10 @@ class RoutedMLP(FeedForward):
         if wd != rt.dtype:
             wd = torch.float32 if rt.dtype == torch.float32 else torch.bfloat16
         self.router = rt.to_device(got[p + "router"], torch.float32)
+        self.rule = None
+        if s.scoring == "sigmoid":
+            self.rule = (rt.to_device(got[p + "correction"], torch.float32) if s.correction else None, float(s.route_scale),
+                         bool(s.renormalize))
         gu = torch.empty((s.experts, s.intermediate_size, 2, s.hidden_size), dtype=wd, device=rt.device)
         down = torch.empty((s.experts, s.hidden_size, s.intermediate_size), dtype=wd, device=rt.device)
         for e in range(s.experts):
@@ -135,7 +149,7 @@ class RoutedMLP(FeedForward):
         tiles = ctx.buf("routed_mlp.tiles", (1 + 2 * ops.moe_max_tiles(mt * top, E, ops.MOE_STREAM_ROWS),), torch.int32)
         act = ctx.buf("routed_mlp.act", (mt * top, s.intermediate_size), rt.dtype)
         y = ctx.buf("routed_mlp.down", (mt * top, s.hidden_size), torch.float32)
-        ops.moe_router(x, self.router, T, top, sel, wgt, stream=ctx.stream)
+        ops.moe_router(x, self.router, T, top, sel, wgt, stream=ctx.stream, rule=self.rule)
         streaming = (T <= self.STREAM_MAX_TOKENS and ops.moe_stream_usable(x, s.hidden_size)
                      and ops.moe_stream_usable(x, s.intermediate_size))
         max_tiles = ops.moe_group(sel, pairs, E, offsets, pair_of_slot, slot_of_pair, tiles,
@@ -149,14 +163,14 @@ class RoutedMLP(FeedForward):
                 lo, n = bounds[e], bounds[e + 1] - bounds[e]
                 if n > 0:
                     ops.gemm_tc(xs[lo:lo + n], self.gate_up[e], gu[lo:lo + n], n, ops.EPI_STORE_F32, err=ctx.err, stream=ctx.stream)
-            ops.moe_activation(gu, act, pairs, s.limit, s.alpha, stream=ctx.stream)
+            ops.moe_activation(gu, act, pairs, self.limit, s.alpha, stream=ctx.stream, up_offset=s.up_offset)
             for e in range(E):
                 lo, n = bounds[e], bounds[e + 1] - bounds[e]
                 if n > 0:
                     ops.gemm_tc(act[lo:lo + n], self.down[e], y[lo:lo + n], n, ops.EPI_STORE_F32, err=ctx.err, stream=ctx.stream)
         else:
-            ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, s.limit, s.alpha, stream=ctx.stream,
-                         streaming=streaming)
+            ops.moe_gemm(x, self.gate_up, act, offsets, pair_of_slot, tiles, max_tiles, top, True, self.limit, s.alpha, stream=ctx.stream,
+                         streaming=streaming, up_offset=s.up_offset)
             ops.moe_gemm(act, self.down, y, offsets, pair_of_slot, tiles, max_tiles, 0, False, stream=ctx.stream, streaming=streaming)
         ops.moe_combine(y, wgt, slot_of_pair, T, top, residual, accumulate=accumulate, stream=ctx.stream)
 

@@ -74,5 +74,41 @@ class LayerNorm(Norm):
                            rounded=rounded, stream=ctx.stream)
 
 
+class DynamicTanh(Norm):
+    """out = tanh(alpha * x) * weight + bias, element by element, fp32: a norm that computes no mean or variance
+    (``alpha`` is a stored scalar).  Being element-wise it can ride on the kernel that sums the copies of a residual
+    stream (``stream_norm``)."""
+
+    graph_safe = True
+
+    def _names(self):
+        s = self.spec
+        return self.prefix + s.weight_suffix, self.prefix + s.bias_suffix, self.prefix + s.alpha_suffix
+
+    def weight_decls(self) -> List[WeightDecl]:
+        w, b, a = self._names()
+        return [WeightDecl(w, (self.spec.size,), init="norm"), WeightDecl(b, (self.spec.size,), init="zeros"),
+                WeightDecl(a, (), init="uniform", lo=0.4, hi=1.2)]
+
+    def load(self, store, rt: Runtime) -> None:
+        w, b, a = self._names()
+        w, b, a = store.take(w, (self.spec.size,)), store.take(b, (self.spec.size,)), store.take(a, ())
+        self.weight = rt.to_device(w, torch.float32) if w is not None else None
+        self.bias = rt.to_device(b, torch.float32) if b is not None else None
+        self.alpha = rt.to_device(a, torch.float32).reshape(1) if a is not None else None
+
+    def scale_output(self, scale: float) -> None:
+        if self.weight is not None:
+            self.weight, self.bias = self.weight * scale, self.bias * scale
+
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+        ops.dynamic_tanh(x, self.alpha, self.weight, self.bias, out, n_rows, rows=rows, stream=ctx.stream)
+
+    def stream_norm(self):
+        """(alpha, weight, bias) for ``ops.stream_read``, which applies the norm to the sum it has just made."""
+        return self.alpha, self.weight, self.bias
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)
 register_part("norm", "layernorm", LayerNorm)

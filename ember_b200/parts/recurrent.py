@@ -3,7 +3,9 @@
 * "channel_delta": delta-rule memory with a decay per head and key channel,
 * "mlstm":         matrix memory with an exponential input gate and a running maximum,
 * "mamba2":        selective state space with a scalar decay per head,
-* "gla":           linear attention with a decay per head and key channel (no convolution, no delta correction).
+* "gla":           linear attention with a decay per head and key channel (no convolution, no delta correction),
+* "wkv":           time mixing: blends with the previous token's input, a data-dependent decay per head and key channel,
+                   a read-out of the state before its update plus a bonus for the current token.
 
 All of them project their input with one fused product whose fp32 result the recurrence kernel reads in place (column
 offsets, no copies), run the same kernels for prompt portions and single tokens (a block walks its run's tokens in
@@ -318,6 +320,89 @@ class GatedLinearAttention(_StateMixer):
         self._out(ctx, y, out, accumulate)
 
 
+# ------------------------------------------------------------------------------------------------- wkv
+class TimeMix(_StateMixer):
+    """With x' the previous token's input (zeros before a request's first token), each of r, k, v, g, w reads its own
+    blend x + (x' - x) mu: r, k, v = W_r, W_k, W_v of theirs (heads x dim), gate = silu(W_g .), and the decay
+    w = exp(-exp(W_w2 tanh(W_w1 .) + w0)) per head and key channel.  Per head, with the bonus u:
+
+        o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T
+
+    then o / rms(o) per head, times norm (all heads' size), times the gate, and the output product.  The state row of a
+    request holds S [heads, dim, dim] and, behind it, the last input x' [hidden]; both start at zero.  Blends are made
+    in fp32 from the input and rounded to the products' dtype; the decay's logits, both exponentials, the bonus and the
+    state are fp32.  Tensors under the prefix: mu.r, mu.k, mu.v, mu.g, mu.w, r, k, v, g, w1, w2, w0, u, norm, o."""
+
+    BLENDS = ("r", "k", "v", "g", "w")
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if min(s.hidden_size, s.num_heads, s.head_dim) <= 0:
+            raise ConfigError("wkv: width, head count and head size must be positive")
+        self.inner = s.num_heads * s.head_dim
+        self.decay_rank = s.decay_rank
+
+    def state_floats(self) -> int:
+        s = self.spec
+        return s.num_heads * s.head_dim * s.head_dim + s.hidden_size
+
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        hid, n, ra = s.hidden_size, self.inner, self.decay_rank
+        if ra <= 0:
+            raise ConfigError("wkv: the rank of the decay projection is read from the weights at load; a configuration "
+                              "that lists tensors without a file must give it")
+        d = [WeightDecl(p + "mu." + b, (hid,), init="uniform", lo=0.0, hi=1.0) for b in self.BLENDS]
+        d += [WeightDecl(p + n_, (n, hid)) for n_ in ("r", "k", "v", "g")]
+        d += [WeightDecl(p + "w1", (ra, hid)), WeightDecl(p + "w2", (n, ra)),
+              WeightDecl(p + "w0", (n,), init="uniform", lo=-3.0, hi=0.5),
+              WeightDecl(p + "u", (s.num_heads, s.head_dim), init="uniform", lo=-0.5, hi=1.0),
+              WeightDecl(p + "norm", (n,), init="norm"), WeightDecl(p + "o", (hid, n))]
+        return d
+
+    def load(self, store, rt: Runtime) -> None:
+        p = self.prefix
+        self.rt = rt
+        if self.decay_rank <= 0:                       # a size the configuration leaves to the weights
+            shape = store.shape(p + "w1")
+            self.decay_rank = int(shape[0]) if shape and len(shape) == 2 else 1
+        w = self._take_all(store)
+        if w is None:
+            return
+        f32 = lambda name: rt.to_device(w[p + name], torch.float32)          # noqa: E731
+        self.mu = torch.stack([f32("mu." + b) for b in self.BLENDS]).contiguous()           # [5, hidden]
+        self.proj = [Linear.from_host(w[p + n], rt) for n in ("r", "k", "v", "g")]
+        self.w1, self.w2, self.o = (Linear.from_host(w[p + n], rt) for n in ("w1", "w2", "o"))
+        self.w0, self.bonus, self.norm_w = f32("w0"), f32("u").reshape(-1).contiguous(), f32("norm")
+        self.one = torch.ones(1, dtype=torch.float32, device=rt.device)
+        self.ones = torch.ones(self.decay_rank, dtype=torch.float32, device=rt.device)
+
+    def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
+        s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
+        H, D, n, hid = s.num_heads, s.head_dim, self.inner, s.hidden_size
+        blends = ctx.buf("wkv.blends", (len(self.BLENDS), mt, hid), rt.dtype)
+        rkvg = ctx.buf("wkv.rkvg", (4, mt, n), torch.float32)
+        low = ctx.buf("wkv.low", (mt, self.decay_rank), torch.float32)
+        low_t = ctx.buf("wkv.low_tanh", (mt, self.decay_rank), rt.dtype)
+        z = ctx.buf("wkv.decay", (mt, n), torch.float32)
+        o = ctx.buf("wkv.read", (mt, n), torch.float32)
+        y = ctx.buf("wkv.normed", (mt, n), rt.dtype)
+        # the previous token's input is the last ``hidden`` floats of the request's state row
+        ops.token_shift(x, self.mu, cache.state, H * D * D, ctx.seq_of, ctx.query_start, ctx.state_slots, blends, T, ctx.S,
+                        stream=ctx.stream)
+        for i, lin in enumerate(self.proj):
+            lin(ctx, blends[i], rkvg[i], T, ops.EPI_STORE_F32)
+        self.w1(ctx, blends[4], low, T, ops.EPI_STORE_F32)
+        ops.dynamic_tanh(low, self.one, self.ones, None, low_t, T, stream=ctx.stream)       # tanh alone
+        self.w2(ctx, low_t, z, T, ops.EPI_STORE_F32)
+        ops.wkv_scan(rkvg, n, 0, mt * n, 2 * mt * n, z, 0, self.w0, self.bonus, cache.state, o, ctx.query_start, ctx.state_slots,
+                     T, ctx.S, H, D, D, stream=ctx.stream)
+        ops.group_norm_gate(o, 0, rkvg[3], 0, self.norm_w, True, s.norm_eps, ops.GATE_SILU_AFTER, y, T, H, D, stream=ctx.stream)
+        self._out(ctx, y, out, accumulate)
+
+
+register_part("mixer", "wkv", TimeMix)
 register_part("mixer", "gla", GatedLinearAttention)
 register_part("mixer", "channel_delta", GatedDelta)
 register_part("mixer", "mlstm", MatrixMemory)

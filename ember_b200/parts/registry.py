@@ -1,6 +1,6 @@
 """Registry from (family, kind) to the class that implements a part.
 
-Families: "norm", "position", "mixer", "feed_forward", "gate", "arrangement".  A layer names its
+Families: "norm", "position", "mixer", "feed_forward", "gate", "connection", "arrangement".  A layer names its
 parts by spec; ``build_part`` looks the class up by the spec's ``kind``.  Registering a new
 class here is all that adding a part takes (no framework file changes).
 """
@@ -11,7 +11,7 @@ from typing import Callable, Dict, Tuple
 from ..config.spec import ConfigError, PartSpec
 
 _PARTS: Dict[Tuple[str, str], Callable] = {}
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "gate", "arrangement")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "gate", "connection", "arrangement")
 
 
 def register_part(family: str, kind: str, cls: Callable) -> None:

@@ -6,7 +6,9 @@
   j <= i with i - j < window or j < keep_first.  Its cache group is of kind "window" with ``keep_first``: pages the
   window has passed go back while the request runs, those of the kept first tokens stay.
 * "latent_attention": queries through a low-rank latent (c_q = RMSNorm(W_dq h), q = W_uq c_q, per head
-  [head_dim unrotated | rot_dim rotated]); W_dkv h = [kv_rank | rot_dim] gives the RMS-normed latent c and a rotated
+  [head_dim unrotated | rot_dim rotated]) or, with ``q_rank`` 0, straight from the input (q = W_q h); the rotated parts
+  turn in neighbouring pairs or in the rotate-half layout, with the position part's frequencies (stretched for long
+  contexts or not) and magnitude; W_dkv h = [kv_rank | rot_dim] gives the RMS-normed latent c and a rotated
   key part shared by the heads; a head's unrotated key is W_uk c and its value W_uv c.  Only [c | rotated part] is
   cached, one row per token (``keys_only``).  The up-projections never touch the cache: with
   q~_h = W_uk[h]^T q_h the score is (q~_h . c + q_rot . k_rot) * scale, and the head's output is W_uv[h] applied to the
@@ -140,23 +142,28 @@ class LatentAttention(_SinkSoftmax):
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         s = spec
-        if min(s.num_heads, s.head_dim, s.value_dim, s.q_rank, s.kv_rank) <= 0 or s.rot_dim < 0:
+        if min(s.num_heads, s.head_dim, s.value_dim, s.kv_rank) <= 0 or s.rot_dim < 0 or s.q_rank < 0:
             raise ConfigError("latent attention: head count, sizes and ranks must be positive")
         if s.kv_rank > 512:
             raise ConfigError(f"latent attention: a latent of {s.kv_rank} (up to 512)")
         self.position = build_part("position", s.position)
         rotary = getattr(s.position, "rotary_dim", 0)
-        if rotary and (getattr(s.position, "layout", "half") != "interleaved" or rotary > s.rot_dim):
-            raise ConfigError("latent attention rotates neighbouring pairs of the rotated part (layout 'interleaved', "
-                              f"at most rot_dim = {s.rot_dim} elements)")
+        if rotary and (getattr(s.position, "layout", "half") not in ("interleaved", "half") or rotary > s.rot_dim):
+            raise ConfigError(f"latent attention rotates at most rot_dim = {s.rot_dim} elements of the rotated part, in the "
+                              "layout 'interleaved' or 'half'")
+        self.half_layout = bool(rotary) and getattr(s.position, "layout", "half") == "half"
+        self.magnitude = float(self.position.magnitude()) if rotary and hasattr(self.position, "magnitude") else 1.0
         self.q_head = s.head_dim + s.rot_dim          # a query head as W_uq makes it
         self.row = s.kv_rank + s.rot_dim              # a cache row, and a query head as the attention reads it
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
         H, hid = s.num_heads, s.hidden_size
-        d = [WeightDecl(p + "dq", (s.q_rank, hid)), WeightDecl(p + "dq.norm", (s.q_rank,), init="norm"),
-             WeightDecl(p + "uq", (H * self.q_head, s.q_rank))]
+        if s.q_rank:
+            d = [WeightDecl(p + "dq", (s.q_rank, hid)), WeightDecl(p + "dq.norm", (s.q_rank,), init="norm"),
+                 WeightDecl(p + "uq", (H * self.q_head, s.q_rank))]
+        else:
+            d = [WeightDecl(p + "q", (H * self.q_head, hid))]
         if s.own_kv:
             d += [WeightDecl(p + "dkv", (self.row, hid)), WeightDecl(p + "dkv.norm", (s.kv_rank,), init="norm")]
         d += [WeightDecl(p + "uk", (H * s.head_dim, s.kv_rank)), WeightDecl(p + "uv", (H * s.value_dim, s.kv_rank))]
@@ -173,20 +180,22 @@ class LatentAttention(_SinkSoftmax):
         got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
         if any(v is None for v in got.values()):
             return
-        wd = rt.weight_dtype(got[p + "dq"].dtype)
+        first = got[p + ("dq" if s.q_rank else "q")]
+        wd = rt.weight_dtype(first.dtype)
         H = s.num_heads
-        # one product for everything that reads the layer's input: [query latent | key/value latent, key part | gate]
-        fused = [got[p + "dq"]] + ([got[p + "dkv"]] if s.own_kv else []) + ([got[p + "g"]] if s.gate else [])
+        # one product for everything that reads the layer's input: [query latent, or the queries themselves | key/value
+        # latent, key part | gate]
+        fused = [first] + ([got[p + "dkv"]] if s.own_kv else []) + ([got[p + "g"]] if s.gate else [])
         self.down = Linear(torch.cat([rt.to_device(t, wd) for t in fused], dim=0).contiguous())
-        self.c_col = s.q_rank
-        self.g_col = s.q_rank + (self.row if s.own_kv else 0)
-        self.uq = Linear.from_host(got[p + "uq"], rt)
+        self.c_col = s.q_rank if s.q_rank else H * self.q_head
+        self.g_col = self.c_col + (self.row if s.own_kv else 0)
+        self.uq = Linear.from_host(got[p + "uq"], rt) if s.q_rank else None
         # per head: [kv_rank, head_dim] (the key up-projection transposed: it multiplies the query) and [value_dim, kv_rank]
         self.uk_t = rt.to_device(got[p + "uk"], wd).view(H, s.head_dim, s.kv_rank).transpose(1, 2).contiguous()
         self.uv = rt.to_device(got[p + "uv"], wd).view(H, s.value_dim, s.kv_rank).contiguous()
         self.o = Linear.from_host(got[p + "o"], rt)
         f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
-        self.dq_norm_w = f32("dq.norm")
+        self.dq_norm_w = f32("dq.norm") if s.q_rank else None
         self.dkv_norm_w = f32("dkv.norm") if s.own_kv else None
         self.sink = f32("sink") if s.sink else None
         self.inv_freq, self.rotary = self.position.rotary_table(rt)
@@ -203,23 +212,28 @@ class LatentAttention(_SinkSoftmax):
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
         H, D, R, V, r = s.num_heads, s.head_dim, s.rot_dim, s.value_dim, s.kv_rank
         a = ctx.buf("latent_attention.down", (mt, self.down.n), torch.float32)
-        cq = ctx.buf("latent_attention.cq", (mt, s.q_rank), rt.dtype)
-        qf = ctx.buf("latent_attention.q", (mt, H * self.q_head), torch.float32)
+        cq = ctx.buf("latent_attention.cq", (mt, s.q_rank), rt.dtype) if s.q_rank else None
         q = ctx.buf("latent_attention.q_latent", (mt, H * self.row), rt.dtype)
         lat = ctx.buf("latent_attention.attended", (mt, H * r), torch.float32)
         og = ctx.buf("latent_attention.out", (mt, H * V), rt.dtype)
         table = ctx.block_table(cache.group)
         write = bool(owns_cache and s.own_kv)
         self.down(ctx, x, a, T, ops.EPI_STORE_F32)
-        ops.latent_prepare(a, 0, s.q_rank, self.c_col, r, R, self.dq_norm_w, self.dkv_norm_w, s.norm_eps, self.inv_freq,
-                           self.rotary, T, ctx.positions, ctx.seq_of, table, cache.page_tokens, cq, cache.k if write else None,
-                           write_kv=write, err=ctx.err, stream=ctx.stream)
-        self.uq(ctx, cq, qf, T, ops.EPI_STORE_F32)
+        if s.q_rank or write:
+            ops.latent_prepare(a, 0, s.q_rank, self.c_col, r, R, self.dq_norm_w, self.dkv_norm_w, s.norm_eps, self.inv_freq,
+                               self.rotary, T, ctx.positions, ctx.seq_of, table, cache.page_tokens, cq, cache.k if write else None,
+                               write_kv=write, err=ctx.err, stream=ctx.stream, half_layout=self.half_layout,
+                               magnitude=self.magnitude)
+        if s.q_rank:
+            qf = ctx.buf("latent_attention.q", (mt, H * self.q_head), torch.float32)
+            self.uq(ctx, cq, qf, T, ops.EPI_STORE_F32)
+        else:
+            qf = a                                  # the queries are the first columns of the fused product
         # a query head as the attention reads it: [W_uk[h]^T q_unrotated | q_rotated]
         ops.head_gemm(qf, self.q_head, 0, self.uk_t, q, self.row, 0, T, stream=ctx.stream)
         if R:
             ops.rotate_pairs(qf, self.q_head, D, q, self.row, r, T, H, R, self.rotary, self.inv_freq, ctx.positions,
-                             stream=ctx.stream)
+                             stream=ctx.stream, half_layout=self.half_layout, magnitude=self.magnitude)
         self._attend(ctx, q, cache.k, None, lat, table, cache.page_tokens, H, 1, self.row, r, 0, 0, self.sink, s.scale)
         ops.head_gemm(lat, r, 0, self.uv, og, V, 0, T, gate=a if s.gate else None, gate_col=self.g_col, stream=ctx.stream)
         self.o(ctx, og, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
