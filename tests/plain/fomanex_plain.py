@@ -173,7 +173,7 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
     eps, mult = float(cfg["norm"]["eps"]), float(cfg.get("residual_mult", 1.0))
     streams = int(cfg.get("streams", 1))
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
-    x = dynamic_tanh(W["embed"][ids] * float(cfg["embedding"]["scale"]), W, "embed.norm")
+    x = dynamic_tanh(W["embed"][ids] * float((cfg.get("embedding") or {}).get("scale", 1.0)), W, "embed.norm")
     X = x[None].repeat(streams, 1, 1)
     for i in layer_order(cfg):
         L, p = cfg["layers"][i], f"l{i}."
@@ -198,6 +198,6 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
         if layers_out is not None:
             layers_out.append(X.sum(0))
     x = dynamic_tanh(X.sum(0), W, "final.norm")
-    logits = lin(x, W["embed"]) * float(cfg["logit_scale"])
+    logits = lin(x, W["embed"]) * float(cfg.get("logit_scale", 1.0))
     cap = float(cfg.get("logit_softcap") or 0.0)
     return cap * torch.tanh(logits / cap) if cap > 0 else logits
