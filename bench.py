@@ -20,6 +20,7 @@ Other workloads of the same engine, one JSON line each (not part of the default 
     python bench.py --workload qwen3-32b     # Qwen3-32B shape: 2,048-token prefill, decode at batch 1 and 8 to 4,096, cache from free memory
     python bench.py --workload fadosun [--breakdown]   # Fadosun beside Qwen3 at equal width, feed-forward and layers
     python bench.py --workload zufusun [--breakdown]   # Zufusun (two of eight experts a token) beside Qwen3 likewise
+    python bench.py --workload fomanex [--breakdown]   # Fomanex beside Zufusun (its closest relative) and Qwen3 likewise
 """
 from __future__ import annotations
 
@@ -362,12 +363,8 @@ def workload_fadosun(args, pk) -> int:
     return beside_qwen3(args, pk, "fadosun", fcfg, n_layers, {"fadosun_layers": [l["type"] for l in FADOSUN_LAYERS]})
 
 
-def workload_zufusun(args, pk) -> int:
-    """Zufusun beside Qwen3 at equal width, vocabulary and number of layers (the 1.7B widths, 8 layers unless --layers
-    says otherwise; random weights), its feed-forward eight experts of half Qwen3's feed-forward size of which a token
-    uses two (the same products per token, four times the weights): the measurements of ``--workload fadosun``."""
+def zufusun_config(n_layers):
     from ember_b200.config import ZufusunConfig
-    n_layers = args.layers or 8
     width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
     mlp = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0}, "router": {"experts": 8, "top": 2}}
     layers = []
@@ -376,15 +373,57 @@ def workload_zufusun(args, pk) -> int:
         if l["mixer"].get("kv_from") == -1:
             l["mixer"]["kv_from"] = i - 1              # the latent of the layer before it
         layers.append(dict(l, mlp=mlp))
-    zcfg = ZufusunConfig.from_json({"architecture": "Zufusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers})
-    return beside_qwen3(args, pk, "zufusun", zcfg, n_layers, {"zufusun_layers": [l["type"] for l in ZUFUSUN_LAYERS],
-                                                             "experts": 8, "top": 2, "expert_ff": ff // 2})
+    return ZufusunConfig.from_json({"architecture": "Zufusun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": layers})
 
 
-def beside_qwen3(args, pk, label, fcfg, n_layers, extra) -> int:
+def workload_zufusun(args, pk) -> int:
+    """Zufusun beside Qwen3 at equal width, vocabulary and number of layers (the 1.7B widths, 8 layers unless --layers
+    says otherwise; random weights), its feed-forward eight experts of half Qwen3's feed-forward size of which a token
+    uses two (the same products per token, four times the weights): the measurements of ``--workload fadosun``."""
+    n_layers = args.layers or 8
+    ff = QWEN3_1P7B["intermediate_size"]
+    return beside_qwen3(args, pk, "zufusun", zufusun_config(n_layers), n_layers,
+                        {"zufusun_layers": [l["type"] for l in ZUFUSUN_LAYERS], "experts": 8, "top": 2, "expert_ff": ff // 2})
+
+
+FOMANEX_LAYERS = [
+    {"type": "wkv", "mixer": {"heads": 16, "dim": 128, "decay_rank": 64}, "mlp": "dense"},
+    {"type": "latent_attention", "mlp": "moe",
+     "mixer": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 0.0722,
+               "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}},
+]
+
+
+def workload_fomanex(args, pk) -> int:
+    """Fomanex beside Zufusun (the design whose latent attention, recurrence and experts are the like kernels) and
+    Qwen3, all at the 1.7B width and vocabulary and with as many layer runs (8 unless --layers says otherwise; random
+    weights).  Time mixing and latent attention alternate, a dense feed-forward of Qwen3's size after the one and eight
+    experts of half that size, two a token, after the other; two copies of the residual stream; of 8 layer runs the
+    third and fourth are one pair of layers run twice (a state and a cache per pass): the measurements of
+    ``--workload fadosun``."""
+    from ember_b200.config import FomanexConfig
+    runs = args.layers or 8
+    looped = 2 * max((runs - 2) // 4, 0)               # layers listed once and run twice (whole wkv + latent pairs)
+    listed = runs - looped
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    mlps = {"dense": {"kind": "dense", "ff": ff},
+            "moe": {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2, "scale": 2.5}}}
+    layers = [dict(json.loads(json.dumps(FOMANEX_LAYERS[i % 2])), mlp=mlps[FOMANEX_LAYERS[i % 2]["mlp"]]) for i in range(listed)]
+    cfg = {"architecture": "Fomanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 45.25},
+           "residual_mult": 0.5, "streams": 2, "logit_scale": 0.25, "logit_softcap": 30.0, "layers": layers}
+    if looped:
+        cfg["loop"] = {"start": 2, "stop": 2 + looped, "times": 2}
+    others = [("zufusun", zufusun_config(runs))]
+    return beside_qwen3(args, pk, "fomanex", FomanexConfig.from_json(cfg), runs,
+                        {"fomanex_layers": [l["type"] for l in FOMANEX_LAYERS], "listed_layers": listed, "loop": cfg.get("loop"),
+                         "streams": 2, "experts": 8, "top": 2, "expert_ff": ff // 2}, others=others)
+
+
+def beside_qwen3(args, pk, label, fcfg, n_layers, extra, others=()) -> int:
     """A design (``fcfg``) and Qwen3 at the 1.7B widths and ``n_layers`` layers, one after the other: prefill of 512 and
     2,048 tokens and decode steps at batch 8 and 64 from a context of 1,024, or with --breakdown the device time per
-    kernel of one 2,048-token prefill and of a decode step at batch 64."""
+    kernel of one 2,048-token prefill and of a decode step at batch 64.  ``others``: (name, configuration) of further
+    models of ``n_layers`` layer runs measured between the two."""
     import torch
     import ember_b200
     from ember_b200 import ops
@@ -454,7 +493,7 @@ def beside_qwen3(args, pk, label, fcfg, n_layers, extra) -> int:
               "page_tokens": PAGE_TOKENS, "peaks": pk["source"]}
     result.update(extra)
     with ClockSampler() as clocks:
-        for name, cfg in ((label, fcfg), ("qwen3", qcfg)):
+        for name, cfg in ((label, fcfg),) + tuple(others) + (("qwen3", qcfg),):
             res = {}
             llm = build(cfg, 64)
             if args.breakdown:
@@ -622,10 +661,10 @@ def main() -> int:
                     help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
-    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun", "zufusun"],
+    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun", "zufusun", "fomanex"],
                     help="default: the Qwen3-1.7B line; serving-8b and qwen3-32b are BASELINE's fourth "
-                         "and fifth configurations; fadosun: that design beside Qwen3 at equal sizes (with --breakdown "
-                         "also per kernel); one JSON line each")
+                         "and fifth configurations; fadosun, zufusun, fomanex: that design beside Qwen3 at equal sizes (with "
+                         "--breakdown also per kernel); one JSON line each")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
     ap.add_argument("--decode-from", type=int, default=DECODE_FROM,
@@ -670,6 +709,8 @@ def main() -> int:
         return workload_fadosun(args, pk)
     if args.workload == "zufusun":
         return workload_zufusun(args, pk)
+    if args.workload == "fomanex":
+        return workload_fomanex(args, pk)
     if args.breakdown:
         return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:

@@ -208,6 +208,81 @@ __global__ void stream_write_kernel(float* __restrict__ X, int S, const float* _
     }
 }
 
+// The same two kernels for up to four copies and rows that are a multiple of four floats on 16-byte boundaries: a thread
+// owns four neighbouring columns of a token in all copies (16-byte loads and stores, the copies' loop unrolled, the mix
+// matrix in registers).  Every element is summed in the order of the kernels above, so the results are the same bits.
+__device__ __forceinline__ void store4(float* out, size_t i4, float4 v) { reinterpret_cast<float4*>(out)[i4] = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* out, size_t i4, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    reinterpret_cast<uint2*>(out)[i4] = u;
+}
+
+template <int S, typename TO>
+__global__ void stream_read_vec_kernel(const float4* __restrict__ X, const float* __restrict__ in_w, const float* __restrict__ alpha,
+                                       const float4* __restrict__ w, const float4* __restrict__ b, TO* __restrict__ out, int H4, size_t n4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const size_t t = idx / H4;
+    const int i = (int)(idx - t * H4);
+    const float4* src = X + t * S * H4 + i;
+    float4 u = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int s = 0; s < S; s++) {
+        const float4 v = src[(size_t)s * H4];
+        const float a = in_w ? in_w[s] : 1.0f;
+        u.x = fmaf(a, v.x, u.x), u.y = fmaf(a, v.y, u.y), u.z = fmaf(a, v.z, u.z), u.w = fmaf(a, v.w, u.w);
+    }
+    if (alpha) {
+        const float a = alpha[0];
+        const float4 ww = w[i], bb = b ? b[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        u.x = fmaf(tanhf(a * u.x), ww.x, bb.x), u.y = fmaf(tanhf(a * u.y), ww.y, bb.y);
+        u.z = fmaf(tanhf(a * u.z), ww.z, bb.z), u.w = fmaf(tanhf(a * u.w), ww.w, bb.w);
+    }
+    store4(out, idx, u);
+}
+
+template <int S>
+__global__ void stream_write_vec_kernel(float4* __restrict__ X, const float* __restrict__ mix, const float* __restrict__ out_w,
+                                        const float4* __restrict__ scale, float multiplier, const float4* __restrict__ y, int H4, size_t n4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    const size_t t = idx / H4;
+    const int i = (int)(idx - t * H4);
+    float4* col = X + t * S * H4 + i;
+    const float4 sc = scale ? scale[i] : make_float4(1.0f, 1.0f, 1.0f, 1.0f), yy = y[idx];
+    const float4 add = make_float4(multiplier * sc.x * yy.x, multiplier * sc.y * yy.y, multiplier * sc.z * yy.z, multiplier * sc.w * yy.w);
+    float4 old[S];
+#pragma unroll
+    for (int s = 0; s < S; s++) old[s] = col[(size_t)s * H4];
+#pragma unroll
+    for (int r = 0; r < S; r++) {
+        float4 v;
+        if (mix) {
+            v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int s = 0; s < S; s++) {
+                const float m = mix[s * S + r];
+                v.x = fmaf(m, old[s].x, v.x), v.y = fmaf(m, old[s].y, v.y), v.z = fmaf(m, old[s].z, v.z), v.w = fmaf(m, old[s].w, v.w);
+            }
+        } else {
+            v = old[r];
+        }
+        const float o = out_w ? out_w[r] : 1.0f;
+        col[(size_t)r * H4] = make_float4(fmaf(o, add.x, v.x), fmaf(o, add.y, v.y), fmaf(o, add.z, v.z), fmaf(o, add.w, v.w));
+    }
+}
+
+static bool aligned16(const void* a, const void* b = nullptr, const void* c = nullptr, const void* d = nullptr, const void* e = nullptr) {
+    return (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)d | (uintptr_t)e) & 15) == 0;
+}
+
 __global__ void stream_spread_kernel(const float* __restrict__ x, float* __restrict__ X, int S, int H, size_t n) {
     pdl_launch_dependents();
     pdl_wait();
@@ -328,6 +403,24 @@ EMBER_API int ember_stream_read(const float* X, int S, const float* in_w, const 
     const size_t n = (size_t)T * H;
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype != EMBER_F32 && out_dtype != EMBER_BF16) return fail("stream_read: unsupported output dtype %d", out_dtype);
+    if (S <= 4 && H % 4 == 0 && aligned16(X, w, b, out)) {
+        const size_t n4 = n / 4;
+        const unsigned vb = (unsigned)((n4 + 255) / 256);
+        const float4 *X4 = (const float4*)X, *w4 = (const float4*)w, *b4 = (const float4*)b;
+#define EMBER_STREAM_READ(S_)                                                                                                      \
+        if (out_dtype == EMBER_F32) launch_kernel(stream_read_vec_kernel<S_, float>, vb, 256, 0, st, X4, in_w, alpha, w4, b4,     \
+                                                  (float*)out, H / 4, n4);                                                         \
+        else launch_kernel(stream_read_vec_kernel<S_, __nv_bfloat16>, vb, 256, 0, st, X4, in_w, alpha, w4, b4, (__nv_bfloat16*)out, H / 4, n4)
+        switch (S) {
+            case 1: EMBER_STREAM_READ(1); break;
+            case 2: EMBER_STREAM_READ(2); break;
+            case 3: EMBER_STREAM_READ(3); break;
+            default: EMBER_STREAM_READ(4); break;
+        }
+#undef EMBER_STREAM_READ
+        return check_launch("stream_read");
+    }
     if (out_dtype == EMBER_F32) launch_kernel(stream_read_kernel<float>, blocks, 256, 0, st, X, S, in_w, alpha, w, b, (float*)out, H, n);
     else if (out_dtype == EMBER_BF16)
         launch_kernel(stream_read_kernel<__nv_bfloat16>, blocks, 256, 0, st, X, S, in_w, alpha, w, b, (__nv_bfloat16*)out, H, n);
@@ -340,6 +433,20 @@ EMBER_API int ember_stream_write(float* X, int S, const float* mix, const float*
     if (T <= 0) return 0;
     if (S <= 0 || S > MAX_STREAMS || H <= 0) return fail("stream_write: %d copies (at most %d) of rows of %d", S, MAX_STREAMS, H);
     const size_t n = (size_t)T * H;
+    if (S <= 4 && H % 4 == 0 && aligned16(X, scale, y)) {
+        const size_t n4 = n / 4;
+        const unsigned vb = (unsigned)((n4 + 255) / 256);
+        cudaStream_t st = (cudaStream_t)stream;
+        float4* X4 = (float4*)X;
+        const float4 *s4 = (const float4*)scale, *y4 = (const float4*)y;
+        switch (S) {
+            case 1: launch_kernel(stream_write_vec_kernel<1>, vb, 256, 0, st, X4, mix, out_w, s4, multiplier, y4, H / 4, n4); break;
+            case 2: launch_kernel(stream_write_vec_kernel<2>, vb, 256, 0, st, X4, mix, out_w, s4, multiplier, y4, H / 4, n4); break;
+            case 3: launch_kernel(stream_write_vec_kernel<3>, vb, 256, 0, st, X4, mix, out_w, s4, multiplier, y4, H / 4, n4); break;
+            default: launch_kernel(stream_write_vec_kernel<4>, vb, 256, 0, st, X4, mix, out_w, s4, multiplier, y4, H / 4, n4); break;
+        }
+        return check_launch("stream_write");
+    }
     launch_kernel(stream_write_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, X, S, mix, out_w, scale, multiplier, y, H, n);
     return check_launch("stream_write");
 }

@@ -75,6 +75,63 @@ __global__ void token_shift_kernel(const TI* __restrict__ x, int C, const float*
     for (int m = 0; m < n_mix; m++) out[m * mix_stride + (size_t)t * C + c] = from_float<TO>(fmaf(d, mu[(size_t)m * C + c], cur));
 }
 
+// The same for rows that are a multiple of 16 bytes on 16-byte boundaries: a thread owns 16 bytes of a token's row
+// (eight bfloat16 or four floats) and writes them to every blend.
+template <typename T> struct Pack16;
+template <> struct Pack16<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float* v) { const float4 a = *reinterpret_cast<const float4*>(p); v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w; }
+    __device__ static void store(float* p, const float* v) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Pack16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float* v) {
+        const uint4 a = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+        for (int j = 0; j < 4; j++) { const float2 f = __bfloat1622float2(h[j]); v[2 * j] = f.x, v[2 * j + 1] = f.y; }
+    }
+    __device__ static void store(__nv_bfloat16* p, const float* v) {
+        uint4 a;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+        for (int j = 0; j < 4; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+        *reinterpret_cast<uint4*>(p) = a;
+    }
+};
+
+template <typename T>
+__global__ void token_shift_vec_kernel(const T* __restrict__ x, int C, const float* __restrict__ mu, int n_mix,
+                                       const float* __restrict__ carry, long long carry_stride, const int* __restrict__ seq_of,
+                                       const int* __restrict__ query_start, const int* __restrict__ slots, T* __restrict__ out,
+                                       size_t mix_stride) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int N = Pack16<T>::N;
+    const int t = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * N;
+    if (c >= C) return;
+    const int s = seq_of[t];
+    float cur[N], d[N], r[N];
+    Pack16<T>::load(x + (size_t)t * C + c, cur);
+    if (t > query_start[s]) {
+        Pack16<T>::load(x + (size_t)(t - 1) * C + c, d);
+    } else {
+        const float* row = carry + (size_t)slots[s] * carry_stride + c;
+#pragma unroll
+        for (int j = 0; j < N; j += 4) Pack16<float>::load(row + j, d + j);
+    }
+#pragma unroll
+    for (int j = 0; j < N; j++) d[j] -= cur[j];
+    for (int m = 0; m < n_mix; m++) {
+        float w[N];
+#pragma unroll
+        for (int j = 0; j < N; j += 4) Pack16<float>::load(mu + (size_t)m * C + c + j, w + j);
+#pragma unroll
+        for (int j = 0; j < N; j++) r[j] = fmaf(d[j], w[j], cur[j]);
+        Pack16<T>::store(out + m * mix_stride + (size_t)t * C + c, r);
+    }
+}
+
 // After the blends: every run's last row becomes its request's carried row.
 template <typename TI>
 __global__ void token_carry_kernel(const TI* __restrict__ x, int C, float* __restrict__ carry, long long carry_stride,
@@ -895,7 +952,20 @@ EMBER_API int ember_token_shift(const void* x, int x_dtype, const float* mu, int
     if (x_dtype != out_dtype || (x_dtype != EMBER_F32 && x_dtype != EMBER_BF16)) return fail("token_shift: dtypes %d -> %d", x_dtype, out_dtype);
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned bx = (unsigned)((C + 127) / 128);
-    if (x_dtype == EMBER_F32) {
+    const int pack = x_dtype == EMBER_F32 ? 4 : 8;
+    const bool vec = C % pack == 0 && carry_stride % 4 == 0 && mix_stride % pack == 0 &&
+                     ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)mu | (uintptr_t)carry) & 15) == 0);
+    const unsigned vx = (unsigned)((C / pack + 127) / 128);
+    if (vec && x_dtype == EMBER_F32) {
+        launch_kernel(token_shift_vec_kernel<float>, dim3(vx, T), 128, 0, st, (const float*)x, C, mu, n_mix, (const float*)carry,
+                      carry_stride, seq_of, query_start, slots, (float*)out, (size_t)mix_stride);
+        launch_kernel(token_carry_kernel<float>, dim3(bx, S), 128, 0, st, (const float*)x, C, carry, carry_stride, query_start, slots);
+    } else if (vec) {
+        launch_kernel(token_shift_vec_kernel<__nv_bfloat16>, dim3(vx, T), 128, 0, st, (const __nv_bfloat16*)x, C, mu, n_mix,
+                      (const float*)carry, carry_stride, seq_of, query_start, slots, (__nv_bfloat16*)out, (size_t)mix_stride);
+        launch_kernel(token_carry_kernel<__nv_bfloat16>, dim3(bx, S), 128, 0, st, (const __nv_bfloat16*)x, C, carry, carry_stride,
+                      query_start, slots);
+    } else if (x_dtype == EMBER_F32) {
         launch_kernel(token_shift_kernel<float, float>, dim3(bx, T), 128, 0, st, (const float*)x, C, mu, n_mix, (const float*)carry,
                       carry_stride, seq_of, query_start, slots, (float*)out, (size_t)mix_stride);
         launch_kernel(token_carry_kernel<float>, dim3(bx, S), 128, 0, st, (const float*)x, C, carry, carry_stride, query_start, slots);
