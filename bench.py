@@ -394,15 +394,11 @@ FOMANEX_LAYERS = [
 ]
 
 
-def workload_fomanex(args, pk) -> int:
-    """Fomanex beside Zufusun (the design whose latent attention, recurrence and experts are the like kernels) and
-    Qwen3, all at the 1.7B width and vocabulary and with as many layer runs (8 unless --layers says otherwise; random
-    weights).  Time mixing and latent attention alternate, a dense feed-forward of Qwen3's size after the one and eight
-    experts of half that size, two a token, after the other; two copies of the residual stream; of 8 layer runs the
-    third and fourth are one pair of layers run twice (a state and a cache per pass): the measurements of
-    ``--workload fadosun``."""
+def fomanex_config(runs):
+    """(configuration, its dictionary) of ``runs`` layer runs: time mixing and latent attention alternate, a dense
+    feed-forward of Qwen3's size after the one and eight experts of half that size, two a token, after the other; two
+    copies of the residual stream; from 6 runs on, pairs of layers behind the first two are listed once and run twice."""
     from ember_b200.config import FomanexConfig
-    runs = args.layers or 8
     looped = 2 * max((runs - 2) // 4, 0)               # layers listed once and run twice (whole wkv + latent pairs)
     listed = runs - looped
     width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
@@ -413,10 +409,20 @@ def workload_fomanex(args, pk) -> int:
            "residual_mult": 0.5, "streams": 2, "logit_scale": 0.25, "logit_softcap": 30.0, "layers": layers}
     if looped:
         cfg["loop"] = {"start": 2, "stop": 2 + looped, "times": 2}
-    others = [("zufusun", zufusun_config(runs))]
-    return beside_qwen3(args, pk, "fomanex", FomanexConfig.from_json(cfg), runs,
-                        {"fomanex_layers": [l["type"] for l in FOMANEX_LAYERS], "listed_layers": listed, "loop": cfg.get("loop"),
-                         "streams": 2, "experts": 8, "top": 2, "expert_ff": ff // 2}, others=others)
+    return FomanexConfig.from_json(cfg), cfg
+
+
+def workload_fomanex(args, pk) -> int:
+    """Fomanex beside Zufusun (the design whose latent attention, recurrence and experts are the like kernels) and
+    Qwen3, all at the 1.7B width and vocabulary and with as many layer runs (8 unless --layers says otherwise; random
+    weights); of 8 layer runs the third and fourth are one pair of layers run twice (a state and a cache per pass): the
+    measurements of ``--workload fadosun``."""
+    runs = args.layers or 8
+    fcfg, cfg = fomanex_config(runs)
+    return beside_qwen3(args, pk, "fomanex", fcfg, runs,
+                        {"fomanex_layers": [l["type"] for l in FOMANEX_LAYERS], "listed_layers": len(cfg["layers"]), "loop": cfg.get("loop"),
+                         "streams": 2, "experts": 8, "top": 2, "expert_ff": QWEN3_1P7B["intermediate_size"] // 2},
+                        others=[("zufusun", zufusun_config(runs))])
 
 
 def beside_qwen3(args, pk, label, fcfg, n_layers, extra, others=()) -> int:

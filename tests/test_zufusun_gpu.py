@@ -415,7 +415,7 @@ def _run_feed_forward(spec, weights, x_all, dtype, portions=(40, 3, 1, 2, 44)):
         part.forward(ctx, x, out, accumulate=False)
         added = torch.ones(256, hidden, device=b.dev)
         part.forward(ctx, x, added, accumulate=True)
-        assert float((added[:n] - 1.0 - out[:n]).abs().max()) < 1e-5
+        assert float((added[:n] - 1.0 - out[:n]).abs().max()) < 1e-6 * (10.0 + float(out[:n].abs().max()))    # a few float32 roundings of the sum
         got[at:at + n] = out[:n].cpu()
         at += n
     return got, part, b
