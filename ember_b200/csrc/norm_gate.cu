@@ -308,14 +308,32 @@ __global__ void stream_sum_kernel(const float* __restrict__ X, const int* __rest
     out[idx] = v;
 }
 
-// logits <- cap * tanh(scale * logits / cap)  (cap 0: scale * logits)
+// logits <- cap * tanh(scale * logits / cap)  (cap 0: scale * logits); four elements a thread where the buffer allows
+__device__ __forceinline__ float capped(float v, float scale, float cap) {
+    v *= scale;
+    return cap > 0.0f ? cap * tanhf(v / cap) : v;
+}
+
 __global__ void logit_finish_kernel(float* __restrict__ logits, float scale, float cap, size_t n) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= n) return;
-    const float v = logits[idx] * scale;
-    logits[idx] = cap > 0.0f ? cap * tanhf(v / cap) : v;
+    logits[idx] = capped(logits[idx], scale, cap);
+}
+
+__global__ void __launch_bounds__(256)
+logit_finish_vec_kernel(float4* __restrict__ logits, float scale, float cap, size_t n4) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n4) return;
+    float4 v = logits[idx];
+    v.x = capped(v.x, scale, cap);
+    v.y = capped(v.y, scale, cap);
+    v.z = capped(v.z, scale, cap);
+    v.w = capped(v.w, scale, cap);
+    logits[idx] = v;
 }
 
 }  // namespace ember
@@ -469,6 +487,11 @@ EMBER_API int ember_stream_sum(const float* X, const int* rows, int S, float* ou
 
 EMBER_API int ember_logit_finish(float* logits, float scale, float cap, long long n, void* stream) {
     if (n <= 0) return 0;
-    launch_kernel(logit_finish_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, logits, scale, cap, (size_t)n);
+    if (n % 4 == 0 && ((uintptr_t)logits & 15) == 0) {
+        const size_t n4 = (size_t)n / 4;
+        launch_kernel(logit_finish_vec_kernel, (unsigned)((n4 + 255) / 256), 256, 0, (cudaStream_t)stream, (float4*)logits, scale, cap, n4);
+    } else {
+        launch_kernel(logit_finish_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, logits, scale, cap, (size_t)n);
+    }
     return check_launch("logit_finish");
 }

@@ -439,6 +439,26 @@ def test_dynamic_tanh_saturates_and_takes_rows():
     assert float((picked.cpu().double() - want[rows.long()]).abs().max()) < 1e-5
 
 
+@pytest.mark.parametrize("n", [1, 7, 4096, 4099, 3 * 257])
+def test_logits_are_scaled_then_capped(n):
+    """cap tanh(scale z / cap) over counts that are and are not a multiple of four (the two forms of the kernel agree to
+    the bit: a logit does not depend on how many rows the step asked for), far beyond the cap, and without a cap."""
+    from ember_b200 import ops
+    dev = torch.device("cuda:0")
+    z = 40.0 * torch.randn(n + 5, generator=torch.Generator().manual_seed(n))
+    z[0] = 1e4
+    for scale, cap in ((1.7, 9.0), (0.25, 30.0), (3.0, 0.0)):
+        buf = z.to(dev)
+        ops.logit_finish(buf, n, scale, cap)
+        want = cap * torch.tanh(scale * z[:n].double() / cap) if cap else scale * z[:n].double()
+        assert float((buf[:n].cpu().double() - want).abs().max()) < 2e-6 * max(cap, 1.0) + (1e-5 * float(z.abs().max()) if not cap else 0.0)
+        assert torch.equal(buf[n:].cpu(), z[n:])                      # nothing behind the count is touched
+        if n >= 4:
+            odd = z.to(dev)[1:]                                       # a start that is not on a 16-byte boundary
+            ops.logit_finish(odd, n - 1, scale, cap)
+            assert torch.equal(odd[:n - 1].cpu(), buf[1:n].cpu())
+
+
 # ------------------------------------------------------------------------ through the programs
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(dtype, dirs, plain_logits, tmp_path):
