@@ -190,9 +190,10 @@ class LatentAttention(_SinkSoftmax):
         self.c_col = s.q_rank if s.q_rank else H * self.q_head
         self.g_col = self.c_col + (self.row if s.own_kv else 0)
         self.uq = Linear.from_host(got[p + "uq"], rt) if s.q_rank else None
-        # per head: [kv_rank, head_dim] (the key up-projection transposed: it multiplies the query) and [value_dim, kv_rank]
-        self.uk_t = rt.to_device(got[p + "uk"], wd).view(H, s.head_dim, s.kv_rank).transpose(1, 2).contiguous()
-        self.uv = rt.to_device(got[p + "uv"], wd).view(H, s.value_dim, s.kv_rank).contiguous()
+        # per head: [kv_rank, head_dim] (the key up-projection transposed: it multiplies the query) and [value_dim, kv_rank];
+        # in the run's dtype (the per-head product has no form for float32 weights between bfloat16 operands)
+        self.uk_t = rt.to_device(got[p + "uk"], rt.dtype).view(H, s.head_dim, s.kv_rank).transpose(1, 2).contiguous()
+        self.uv = rt.to_device(got[p + "uv"], rt.dtype).view(H, s.value_dim, s.kv_rank).contiguous()
         self.o = Linear.from_host(got[p + "o"], rt)
         f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
         self.dq_norm_w = f32("dq.norm") if s.q_rank else None

@@ -97,3 +97,68 @@ def plain_inputs(model_dir: str):
         cfg = json.load(f)
     W = read_safetensors(os.path.join(model_dir, "model.safetensors"))
     return cfg, {k: (v.double() if v.is_floating_point() else v) for k, v in W.items()}
+
+
+def drawn_fomanex(seed: int) -> dict:
+    """A configuration drawn from a seed: 3 to 7 layers of either mixer in any order, any feed-forward or none, head
+    counts and sizes from short lists that include ones no tensor-core kernel takes, 1 to 8 copies of the stream, a looped
+    stretch anywhere (also empty, also a single pass), constants from short lists."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    pick = lambda *v: v[int(rng.integers(0, len(v)))]                         # noqa: E731
+    width, n = pick(128, 192, 256, 384, 448, 136, 200), int(rng.integers(3, 8))
+    layers = []
+    for _ in range(n):
+        if rng.random() < 0.5:
+            dim, rot_dim = pick(16, 24, 32, 48, 64, 96, 128), pick(8, 16, 32, 64, 4, 24)
+            rot = {"dims": rot_dim, "base": pick(10000.0, 500000.0, 1e6, 50000.0)}
+            if rng.random() < 0.8:
+                rot["scaling"] = {"factor": pick(2.0, 4.0, 8.0, 16.0, 40.0), "original": pick(64, 128, 256, 512, 4096),
+                                  "fast": pick(32.0, 16.0, 8.0), "slow": pick(1.0, 2.0, 0.5)}
+            mixer = _latent(pick(2, 3, 4, 5, 8, 12), dim, rot_dim, pick(16, 32, 48, 96, 128, dim), pick(32, 48, 96, 128, 160, 256, 40),
+                            float((dim + rot_dim) ** -0.5 * pick(1.0, 0.7, 1.5)), rot)
+            kind = "latent_attention"
+        else:
+            mixer = {"heads": pick(1, 2, 4, 5, 8), "dim": pick(16, 32, 64, 80, 96, 128, 24), "decay_rank": pick(8, 16, 24, 32, 64, 12)}
+            kind = "wkv"
+        k = rng.random()
+        if k < 0.4:
+            mlp = _dense(pick(128, 256, 512, 768, 200))
+        elif k < 0.9:
+            e = pick(4, 8, 16, 32, 64, 6)
+            mlp = _moe(pick(32, 64, 128, 192, 40), e, int(rng.integers(1, min(e, 8) + 1)), pick(1.0, 1.5, 2.5, 0.5))
+        else:
+            mlp = None
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Fomanex", "vocab": pick(384, 512, 640, 768, 1000, 333), "width": width, "norm": {"eps": pick(1e-5, 1e-6)},
+           "embedding": {"scale": float(width ** 0.5 * pick(1.0, 0.5))}, "residual_mult": pick(0.5, 1.0, 0.3, 0.7),
+           "streams": pick(1, 2, 3, 4, 6, 8), "logit_scale": pick(1.0, 2.0, 0.5, 4.0), "logit_softcap": pick(15.0, 30.0, 50.0, 8.0),
+           "layers": layers}
+    if rng.random() < 0.85:
+        a = int(rng.integers(0, n))
+        cfg["loop"] = {"start": a, "stop": int(rng.integers(a, n + 1)), "times": int(rng.integers(1, 4))}
+    return cfg
+
+
+def write_drawn_dir(seed: int, out_dir: str) -> str:
+    """A folder for ``drawn_fomanex(seed)`` with random weights whose mix matrices are scaled so that every copy of the
+    stream stays a weighted mean of the old ones (columns sum to 1): over a dozen runs the copies keep their size, and
+    float32 rounding stays where the arithmetic puts it."""
+    from ember_b200.config import FomanexConfig
+    from ember_b200.weights import write_model_dir
+    from ember_b200.weights.safetensors_io import save_file
+    from tests.plain.qwen3_plain import read_safetensors
+    cfg = drawn_fomanex(seed)
+    write_model_dir(FomanexConfig.from_json(cfg), out_dir, seed=seed, dtype=torch.bfloat16)
+    path = os.path.join(out_dir, "model.safetensors")
+    W = read_safetensors(path)
+    for name in W:
+        if name.endswith(".mix"):
+            W[name] = (W[name].float() / W[name].float().sum(0, keepdim=True)).bfloat16()
+    save_file({k: (v.bfloat16() if v.is_floating_point() else v) for k, v in W.items()}, path)      # stored as written: bfloat16
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        c = json.loads(json.dumps(cfg))
+        for l in c["layers"]:
+            l["mixer"].pop("decay_rank", None)
+        json.dump(c, f)
+    return out_dir

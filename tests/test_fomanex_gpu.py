@@ -91,6 +91,41 @@ def test_replay_modes(name, dtype, mode, page, dirs, plain_logits):
     assert_close(collect(steps, outputs), plain_logits(name, requests), dtype, f"{name} {mode}")
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Layer orders, sizes, head counts, copies, loops and constants drawn from a seed: whole prompts, portions and a
+    mixed batch in float32 (the sharper comparison), the mixed batch in bfloat16."""
+    from tests.fomanex_configs import drawn_fomanex, write_drawn_dir
+    d = write_drawn_dir(seed, str(tmp_path))
+    inputs = plain_inputs(d)
+    rng = np.random.default_rng(100 + seed)
+    vocab = drawn_fomanex(seed)["vocab"]
+    requests = {f"r{i}": rng.integers(0, vocab, size=n).tolist() for i, n in enumerate((1, 2, int(rng.integers(30, 90)), int(rng.integers(100, 200)), 47, 19))}
+    want = {rid: plain.forward(*inputs, toks).numpy() for rid, toks in requests.items()}
+    for dtype, modes in (("float32", ("whole", "portions", "mixed")), ("bfloat16", ("mixed",))):
+        for mode in modes:
+            steps = {"whole": trace_whole, "portions": lambda r: trace_portions(r, sizes=(7, 2, 19, 1, 3, 33, 2, 16, 5, 64)),
+                     "mixed": lambda r: trace_mixed(r, live=4, seed=seed)}[mode](requests)
+            page = (16, 64)[seed % 2]
+            outputs, _ = replay(d, dtype, steps, max_live_tokens(steps, round_to=page), page_tokens=page)
+            assert_close(collect(steps, outputs), want, dtype, f"drawn {seed} {mode}")
+
+
+@pytest.mark.parametrize("name", ["p", "q"])
+def test_weights_stored_in_float32_serve_a_bfloat16_run(name, tmp_path, plain_logits, dirs):
+    """The same values stored as float32: products keep the stored precision where they have a form for it and round
+    to bfloat16 where they do not; either way the run is the bfloat16 one to rounding."""
+    from ember_b200.weights.safetensors_io import save_file
+    from tests.plain.qwen3_plain import read_safetensors
+    d = write_fomanex_dir(name, str(tmp_path))
+    path = os.path.join(d, "model.safetensors")
+    save_file({k: (v.float() if v.is_floating_point() else v) for k, v in read_safetensors(path).items()}, path)
+    requests = make_requests(name, (2, 50, 90), seed=8)
+    steps = trace_portions(requests, sizes=(33, 2, 1, 16))
+    outputs, _ = replay(d, "bfloat16", steps, 192)
+    assert_close(collect(steps, outputs), plain_logits(name, requests), "bfloat16", "float32 weights")
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_through_graphs_equals_the_prompt(dtype, dirs, plain_logits):
     """300 tokens one by one (captured graphs after the second step; every pass of the looped layers, the router's
