@@ -629,7 +629,13 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
     const int nh = min(p.head_chunk, group - hc * p.head_chunk);
     const int seq = p.tiles[tile * 4 + 0], row0 = p.tiles[tile * 4 + 1], nq = p.tiles[tile * 4 + 2], pos0 = p.tiles[tile * 4 + 3];
     const int rows = nq * nh;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wr = warp & 3, wc = warp >> 2;
+    // Warps: four row slabs of 16 rows, two warps a slab with half of the value columns each.  A tile of at most 16 rows
+    // (a decoded token's heads) would leave three slabs idle and two warps with all the work, and a warp's chain of
+    // dependent instructions per key tile is what bounds the block: there all eight warps take the one slab and an eighth
+    // of the value columns each (every warp computes the slab's scores, as the two of a slab do anyway).  A value
+    // column's sums are the same instructions in the same order either way.
+    const bool narrow = rows <= 16 && DV % 128 == 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wr = narrow ? 0 : warp & 3, wc = narrow ? warp : warp >> 2;
     const int g = lane >> 2, t = lane & 3;
     const __nv_bfloat16* q = (const __nv_bfloat16*)p.q;
     const __nv_bfloat16* kp = (const __nv_bfloat16*)p.k_pool;
@@ -651,7 +657,7 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
     const int rA = wr * 16 + g, rB = rA + 8;                   // the thread's two rows
     const int qposA = pos0 + rA / nh, qposB = pos0 + rB / nh;
     const bool liveA = rA < rows, liveB = rB < rows;
-    const int half = DV / 2, col0 = wc * half;                 // the warp's value columns
+    const int half = narrow ? DV / 8 : DV / 2, col0 = wc * half;      // the warp's value columns
 
     float mA = -INFINITY, mB = -INFINITY, lA = 0.0f, lB = 0.0f;
     float o[NTO][4];
