@@ -9,6 +9,7 @@ from .qwen3 import Qwen3Config
 from .fadosun import FadosunConfig
 from .zufusun import ZufusunConfig
 from .fomanex import FomanexConfig
+from .pepapel import PepapelConfig
 
 __all__ = [
     "AttentionSpec", "ConfigError", "GatedMLPSpec", "LayerSpec", "ModelSpec", "NoPositionSpec", "PartSpec",
@@ -17,5 +18,5 @@ __all__ = [
     "Qwen3Config", "FadosunConfig", "GatedDeltaSpec", "LayerNormSpec", "MatrixMemorySpec", "ParallelMixerSpec",
     "SigmoidAttentionSpec", "SigmoidGateSpec", "StateSpaceSpec", "ZufusunConfig", "GatedLinearAttentionSpec",
     "LatentAttentionSpec", "RoutedMLPSpec", "SinkAttentionSpec", "FomanexConfig", "DynamicTanhSpec", "HyperConnectionSpec",
-    "TimeMixSpec",
+    "TimeMixSpec", "PepapelConfig",
 ]

@@ -49,6 +49,7 @@ class LayerNormSpec(PartSpec):
     eps: float = 1e-5
     weight_suffix: str = "weight"
     bias_suffix: str = "bias"
+    bias: bool = True             # False: a weight and no bias (no tensor under ``bias_suffix``)
 
 
 @dataclass(frozen=True)
@@ -86,6 +87,8 @@ class RotarySpec(PartSpec):
     scaling_original: float = 0.0
     scaling_fast: float = 32.0
     scaling_slow: float = 1.0
+    # Linear scaling (position interpolation): every frequency is divided by ``linear_factor``, nothing else changes.
+    linear_factor: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -145,7 +148,16 @@ class SinkAttentionSpec(PartSpec):
     number per head without key or value, tensor ``sink``).  Keys and values may differ in size.  ``qk_norm`` "whole":
     one RMS norm over the whole query projection and one over the whole key projection (tensors ``q.norm``, ``k.norm``
     of that size), "none": no norm.  ``window`` > 0: position i sees j <= i with i - j < window or j < keep_first.
-    ``bias``: q, k and v have biases (``q.b`` ...).  Tensors: q, k, v, o."""
+    ``bias``: q, k and v have biases (``q.b`` ...).  Tensors: q, k, v, o.
+
+    Options that other designs turn on, each alone or together: ``qk_norm`` "head" (an RMS norm per head, weights of
+    ``head_dim`` shared by the heads); ``conv_taps`` > 0 (a short causal convolution over time on every channel of q,
+    k and v, tensors ``q.conv`` ... [channels, taps], straight after the projection; the last taps - 1 projected rows
+    are a per-request state); ``position`` (a rotation of queries and keys after the norm); ``q_temp_every`` > 0 (the
+    query at position p is multiplied by 1 + q_temp_coef * ln(floor((p + 1) / q_temp_every) + 1)); ``softcap`` > 0
+    (score <- softcap * tanh(score / softcap) after the scale); ``chunk`` > 0 (position i sees j <= i only if
+    floor(i / chunk) == floor(j / chunk), chunks counted from the sequence's start); ``head_gate`` (head h's output is
+    multiplied by sigmoid(W_g x)_h, tensor ``g`` [heads, hidden])."""
 
     kind: ClassVar[str] = "sink_attention"
     hidden_size: int = 0
@@ -160,6 +172,13 @@ class SinkAttentionSpec(PartSpec):
     window: int = 0
     keep_first: int = 0
     sink: bool = True
+    conv_taps: int = 0
+    position: PartSpec = field(default_factory=NoPositionSpec)
+    q_temp_coef: float = 0.0
+    q_temp_every: int = 0
+    softcap: float = 0.0
+    chunk: int = 0
+    head_gate: bool = False
 
 
 @dataclass(frozen=True)
@@ -224,7 +243,11 @@ class TimeMixSpec(PartSpec):
 class GatedDeltaSpec(PartSpec):
     """Delta-rule memory with a decay per head and key channel: short convolutions + silu on q, k, v, unit-length
     q and k, a write strength per head, low-rank projections for the decay and for the output gate.
-    ``decay_rank`` / ``gate_rank`` 0: read from the stored tensors' shapes."""
+    ``decay_rank`` / ``gate_rank`` 0: read from the stored tensors' shapes.
+
+    ``decay`` "head": one decay per head, g = exp(-exp(A_log[h]) softplus(W_a x + dt_bias[h])) with a full-rank
+    projection ``a`` [heads, hidden] (no a1 / a2, ``dt_bias`` [heads]).  ``gate`` "silu": the normed read-out is
+    multiplied by silu(W_g x) with a full-rank ``g`` [heads vdim, hidden] (no g1 / g2) instead of the low-rank sigmoid gate."""
 
     kind: ClassVar[str] = "channel_delta"
     hidden_size: int = 0
@@ -237,6 +260,8 @@ class GatedDeltaSpec(PartSpec):
     gate_rank: int = 0
     norm_eps: float = 1e-6
     key_eps: float = 1e-6         # inside the root of the unit norm of q and k
+    decay: str = "channel"        # "channel" | "head"
+    gate: str = "low_rank_sigmoid"   # "low_rank_sigmoid" | "silu"
 
 
 @dataclass(frozen=True)
@@ -275,7 +300,9 @@ class StateSpaceSpec(PartSpec):
 
 @dataclass(frozen=True)
 class ParallelMixerSpec(PartSpec):
-    """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right.  ``branch_norm``:
+    each result is first RMS-normed over the model width with a weight of its own (tensors ``left_norm_name`` and
+    ``right_norm_name`` under the mixer's prefix, eps ``norm_eps``)."""
 
     kind: ClassVar[str] = "parallel"
     hidden_size: int = 0
@@ -285,6 +312,10 @@ class ParallelMixerSpec(PartSpec):
     right_scale: float = 1.0
     left_prefix: str = "left."
     right_prefix: str = "right."
+    branch_norm: bool = False
+    norm_eps: float = 1e-6
+    left_norm_name: str = "left.out"
+    right_norm_name: str = "right.out"
 
 
 # ----------------------------------------------------------------------------- gates
@@ -310,6 +341,13 @@ class GatedMLPSpec(PartSpec):
     intermediate_size: int = 0
     activation: str = "silu"
     names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+    # ``activation`` "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), g sigmoid(alpha g) (u + up_offset).
+    limit: float = 0.0
+    alpha: float = 1.702
+    up_offset: float = 1.0
+    # ``bias``: the three projections have biases, named like the matrices with ``bias_suffix`` behind.
+    bias: bool = False
+    bias_suffix: str = ".b"
 
 
 @dataclass(frozen=True)
@@ -335,6 +373,16 @@ class RoutedMLPSpec(PartSpec):
     correction: bool = False
     route_scale: float = 1.0
     renormalize: bool = False
+    # ``scoring`` "softmax": s = softmax(logits) over all router outputs, otherwise like "sigmoid".
+    # ``groups`` > 0: the router's outputs form that many equal groups of neighbours; a group's score is its largest
+    # s + correction, and only outputs of the ``keep_groups`` best groups can be chosen.
+    groups: int = 0
+    keep_groups: int = 0
+    # ``identity`` > 0: the router has ``experts`` + ``identity`` outputs; the last ``identity`` are experts without
+    # tensors whose output is the token's input itself (times the weight).
+    identity: int = 0
+    # ``expert`` "gated" as above, or "square_relu": W_down relu(W_up h)^2, tensors e<i>.up and e<i>.down only.
+    expert: str = "gated"
 
 
 # ---------------------------------------------------------------------- connections
@@ -368,6 +416,9 @@ class LayerSpec:
 
     arrangement: str = "prenorm"
     parts: Tuple[Tuple[str, PartSpec, str], ...] = ()
+    # numbers that belong to the arrangement itself and to none of its parts, by name (a post-norm layer's multiplier
+    # of the stream, for instance)
+    constants: Tuple[Tuple[str, float], ...] = ()
 
     def __post_init__(self):
         roles = [r for r, _, _ in self.parts]
@@ -376,6 +427,12 @@ class LayerSpec:
 
     def roles(self) -> Tuple[str, ...]:
         return tuple(r for r, _, _ in self.parts)
+
+    def constant(self, name: str, default: float) -> float:
+        for n, v in self.constants:
+            if n == name:
+                return float(v)
+        return float(default)
 
     def part(self, role: str) -> Tuple[PartSpec, str]:
         for r, spec, prefix in self.parts:

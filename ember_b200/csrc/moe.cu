@@ -31,8 +31,11 @@ constexpr int MOE_BM = 32, MOE_BN = 64, MOE_BK = 16;
 // How the chosen experts are found and weighed.  sigmoid 0: by the logits, weights = softmax over the chosen logits
 // alone.  sigmoid 1: scores s = sigmoid(logit); the choice is by s + correction[e] (correction may be null), the
 // weights are the chosen experts' s times scale, divided by their sum first if renormalize.
+// sigmoid 2: scores s = softmax(logits) over all experts, otherwise as sigmoid 1.  groups > 0 (at most 32): the experts
+// form `groups` equal groups of neighbours, a group's score is its largest s + correction, and only experts of the
+// `keep` best groups (ties: the lower index) can be chosen.
 struct RouteRule {
-    int sigmoid; const float* correction; float scale; int renormalize;
+    int sigmoid; const float* correction; float scale; int renormalize; int groups; int keep;
 };
 
 // One warp a token.  A lane holds experts lane, lane + 32, ... in z.
@@ -99,11 +102,54 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
                                                float* __restrict__ wgt, int t, int lane, const RouteRule& rule) {
     float score[MOE_MAX_EXPERTS / 32];                      // sigmoid rule: s of the lane's experts; z becomes what is compared
     if (rule.sigmoid) {
+        float zmax = -INFINITY, zsum = 0.0f;
+        if (rule.sigmoid == 2) {                            // softmax over all experts
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+                if (lane + 32 * i < E) zmax = fmaxf(zmax, z[i]);
+            zmax = warp_max(zmax);
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+                if (lane + 32 * i < E) zsum += expf(z[i] - zmax);
+            zsum = warp_sum(zsum);
+        }
 #pragma unroll
         for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
             const int e = lane + 32 * i;
-            score[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.0f;
+            if (rule.sigmoid == 2) score[i] = e < E ? expf(z[i] - zmax) / zsum : 0.0f;
+            else score[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.0f;
             if (e < E) z[i] = score[i] + (rule.correction ? rule.correction[e] : 0.0f);
+        }
+        if (rule.groups > 0) {                              // lane g keeps group g's best; then the best groups, one by one
+            const int per = E / rule.groups;
+            float gbest = -INFINITY;
+            for (int g = 0; g < rule.groups; g++) {
+                float b = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                    const int e = lane + 32 * i;
+                    if (e < E && e / per == g) b = fmaxf(b, z[i]);
+                }
+                b = warp_max(b);
+                if (lane == g) gbest = b;
+            }
+            unsigned kept = 0u;
+            for (int k = 0; k < rule.keep; k++) {
+                float b = (lane < rule.groups && !((kept >> lane) & 1u)) ? gbest : -INFINITY;
+                int at = (lane < rule.groups && !((kept >> lane) & 1u)) ? lane : 0x7fffffff;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ob = __shfl_xor_sync(0xffffffffu, b, o);
+                    const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                    if (oa != 0x7fffffff && (at == 0x7fffffff || ob > b || (ob == b && oa < at))) { b = ob; at = oa; }
+                }
+                if (at != 0x7fffffff) kept |= 1u << at;
+            }
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                const int e = lane + 32 * i;
+                if (e < E && !((kept >> (e / per)) & 1u)) z[i] = -INFINITY;
+            }
         }
     }
     float first = 0.0f, sum = 0.0f, mine = 0.0f;            // lane k keeps the k-th choice's weight (top <= 32)
@@ -153,7 +199,7 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
 __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ sel, int n_pairs, int E, int* __restrict__ offsets,
                                                          int* __restrict__ pair_of_slot, int* __restrict__ slot_of_pair,
                                                          int* __restrict__ n_tiles, int* __restrict__ tile_expert,
-                                                         int* __restrict__ tile_row0, int max_tiles, int tile_rows) {
+                                                         int* __restrict__ tile_row0, int max_tiles, int tile_rows, int tiled) {
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], cursor[MOE_MAX_EXPERTS], tstart[MOE_MAX_EXPERTS + 1];
     pdl_launch_dependents();
     pdl_wait();
@@ -166,7 +212,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__
         for (int e = 0; e < E; e++) {
             start[e] = at; tstart[e] = tt;
             at += count[e];
-            tt += (count[e] + tile_rows - 1) / tile_rows;
+            if (e < tiled) tt += (count[e] + tile_rows - 1) / tile_rows;     // experts from `tiled` on have no weights: slots, no tiles
         }
         start[E] = at; tstart[E] = tt;
         *n_tiles = tt < max_tiles ? tt : max_tiles;
@@ -200,7 +246,10 @@ struct MoeGemmArgs {
     int top;                             // > 0: row of x = pair / top (a token); 0: row of x = slot
     int N, K;
     float limit, alpha, up_offset;      // (limit may be +inf: no clamps)
+    int act;                            // ungated product: 0 stores the sums, 1 stores relu(sum)^2
 };
+
+__device__ __forceinline__ float plain_act(float v, int act) { return act == 1 ? (v > 0.0f ? v * v : 0.0f) : v; }
 
 // GATED: N counts interleaved (gate, up) rows, the output has N / 2 columns.
 template <typename TX, typename TW, typename TO, bool GATED>
@@ -266,7 +315,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs p) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int n = n0 + tx * 4 + j;
-                if (n < p.N) o[n] = from_float<TO>(acc[i][j]);
+                if (n < p.N) o[n] = from_float<TO>(plain_act(acc[i][j], p.act));
             }
         }
     }
@@ -335,8 +384,8 @@ __device__ __forceinline__ void moe_stream_rows(const MoeGemmArgs& p, const uint
                 const float g = fminf(v0, p.limit), u = fminf(fmaxf(v1, -p.limit), p.limit);
                 o[pr] = from_float<TO>(g / (1.0f + expf(-p.alpha * g)) * (u + p.up_offset));
             } else {
-                o[n0] = from_float<TO>(v0);
-                if (two) o[n0 + 1] = from_float<TO>(v1);
+                o[n0] = from_float<TO>(plain_act(v0, p.act));
+                if (two) o[n0 + 1] = from_float<TO>(plain_act(v1, p.act));
             }
         }
     }
@@ -463,7 +512,7 @@ __global__ void __launch_bounds__(MT_WARPS * 32) moe_stream_tc_kernel(MoeGemmArg
                         ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + (n >> 1)] = from_float<TO>(gt / (1.0f + expf(-p.alpha * gt)) * (u + p.up_offset));
                     }
                 } else if (n < p.N && slot < rows) {
-                    ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + n] = from_float<TO>(v);
+                    ((TO*)p.out)[(size_t)(row0 + slot) * p.ld_o + n] = from_float<TO>(plain_act(v, p.act));
                 }
             }
 }
@@ -482,25 +531,43 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __rest
 // act[slot, j] = g sigmoid(alpha g) (u + 1), g = min(gu[slot, 2j], limit), u = clamp(gu[slot, 2j + 1], -limit, limit).
 template <typename TO>
 __global__ void moe_activation_kernel(const float2* __restrict__ gu, TO* __restrict__ act, size_t n, float limit, float alpha,
-                                      float up_offset) {
+                                      float up_offset, const float2* __restrict__ bias, int ff) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float2 v = gu[i];
+    float2 v = gu[i];
+    if (bias) { const float2 b = bias[i % ff]; v.x += b.x; v.y += b.y; }       // (gate, up) biases, interleaved like the rows
     const float g = fminf(v.x, limit), u = fminf(fmaxf(v.y, -limit), limit);
     act[i] = from_float<TO>(g / (1.0f + expf(-alpha * g)) * (u + up_offset));
 }
 
+// act[i] = relu(x[i])^2: the activation of an ungated expert whose product left fp32 sums.
+template <typename TO>
+__global__ void moe_square_relu_kernel(const float* __restrict__ x, TO* __restrict__ act, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i];
+    act[i] = from_float<TO>(v > 0.0f ? v * v : 0.0f);
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ wgt, const int* __restrict__ slot_of_pair,
-                                   int top, float* __restrict__ out, int accumulate, int hidden) {
+                                   int top, float* __restrict__ out, int accumulate, int hidden, const int* __restrict__ sel,
+                                   int experts, const float* __restrict__ same_f, const __nv_bfloat16* __restrict__ same_h) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float s = 0.0f;
-        for (int k = 0; k < top; k++)
-            s = fmaf(wgt[(size_t)t * top + k], y[(size_t)slot_of_pair[(size_t)t * top + k] * hidden + i], s);
+        for (int k = 0; k < top; k++) {
+            // a choice from `experts` on is an identity expert: its output is the token's input row itself
+            const bool same = sel && sel[(size_t)t * top + k] >= experts;
+            const float v = same ? (same_f ? same_f[(size_t)t * hidden + i] : to_float(same_h[(size_t)t * hidden + i]))
+                                 : y[(size_t)slot_of_pair[(size_t)t * top + k] * hidden + i];
+            s = fmaf(wgt[(size_t)t * top + k], v, s);
+        }
         out[(size_t)t * hidden + i] = accumulate ? out[(size_t)t * hidden + i] + s : s;
     }
 }
@@ -512,19 +579,22 @@ using namespace ember;
 EMBER_API int ember_moe_tile_rows() { return MOE_BM; }
 
 EMBER_API int ember_moe_route(const float* logits, int T, int E, int top, int* sel, float* wgt, int sigmoid, const float* correction,
-                              float scale, int renormalize, void* stream) {
+                              float scale, int renormalize, int groups, int keep, void* stream) {
     if (T <= 0) return 0;
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32)
         return fail("moe_route: top %d of %d experts (at most 32 of %d)", top, E, MOE_MAX_EXPERTS);
     launch_kernel(moe_route_kernel, (unsigned)((T + 7) / 8), 256, 0, (cudaStream_t)stream, logits, E, top, sel, wgt, T,
-                  RouteRule{sigmoid, correction, scale, renormalize});
+                  RouteRule{sigmoid, correction, scale, renormalize, groups, keep});
     return check_launch("moe_route");
 }
 
 EMBER_API int ember_moe_router(const void* x, int x_dtype, const float* w, int T, int K, int E, int top, int* sel, float* wgt,
-                               float* logits, int sigmoid, const float* correction, float scale, int renormalize, void* stream) {
+                               float* logits, int sigmoid, const float* correction, float scale, int renormalize, int groups, int keep,
+                               void* stream) {
     if (T <= 0) return 0;
-    const RouteRule rule{sigmoid, correction, scale, renormalize};
+    const RouteRule rule{sigmoid, correction, scale, renormalize, groups, keep};
+    if (groups < 0 || groups > 32 || (groups > 0 && (!sigmoid || E % groups || keep < 1 || keep > groups || top > keep * (E / groups))))
+        return fail("moe_router: %d groups of which %d are kept, for top %d of %d experts", groups, keep, top, E);
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32 || K <= 0)
         return fail("moe_router: top %d of %d experts (at most 32 of %d), rows of %d", top, E, MOE_MAX_EXPERTS, K);
     cudaStream_t st = (cudaStream_t)stream;
@@ -537,22 +607,22 @@ EMBER_API int ember_moe_router(const void* x, int x_dtype, const float* w, int T
 }
 
 EMBER_API int ember_moe_group(const int* sel, int n_pairs, int E, int* offsets, int* pair_of_slot, int* slot_of_pair, int* n_tiles,
-                              int* tile_expert, int* tile_row0, int max_tiles, int tile_rows, void* stream) {
+                              int* tile_expert, int* tile_row0, int max_tiles, int tile_rows, int tiled, void* stream) {
     if (n_pairs <= 0) return 0;
     if (tile_rows != MOE_BM && tile_rows != MS_ROWS) return fail("moe_group: tiles of %d rows (%d or %d)", tile_rows, MOE_BM, MS_ROWS);
     if (E <= 0 || E > MOE_MAX_EXPERTS || max_tiles < n_pairs / tile_rows + E) return fail("moe_group: %d experts, room for %d tiles", E, max_tiles);
     launch_kernel(moe_group_kernel, 1, 1024, 0, (cudaStream_t)stream, sel, n_pairs, E, offsets, pair_of_slot, slot_of_pair, n_tiles,
-                  tile_expert, tile_row0, max_tiles, tile_rows);
+                  tile_expert, tile_row0, max_tiles, tile_rows, (tiled <= 0 || tiled > E) ? E : tiled);
     return check_launch("moe_group");
 }
 
 EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
                              int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
                              const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
-                             float limit, float alpha, float up_offset, void* stream) {
+                             float limit, float alpha, float up_offset, int act, void* stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_gemm: N=%d K=%d", N, K);
-    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset};
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset, act};
     dim3 grid(max_tiles, (N + MOE_BN - 1) / MOE_BN);
     cudaStream_t st = (cudaStream_t)stream;
     const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
@@ -563,6 +633,7 @@ EMBER_API int ember_moe_gemm(const void* x, int x_dtype, int ld_x, const void* w
     } else {
         if (key == 0) launch_kernel(moe_gemm_kernel<float, float, float, false>, grid, 256, 0, st, p);
         else if (key == 110) launch_kernel(moe_gemm_kernel<__nv_bfloat16, __nv_bfloat16, float, false>, grid, 256, 0, st, p);
+        else if (key == 111) launch_kernel(moe_gemm_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, false>, grid, 256, 0, st, p);
         else return fail("moe_gemm: unsupported dtypes %d", key);
     }
     return check_launch("moe_gemm");
@@ -575,14 +646,14 @@ EMBER_API int ember_moe_stream_rows() { return MS_ROWS; }
 EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void* w, int w_dtype, long long w_expert, void* out,
                                int out_dtype, int ld_o, const int* offsets, const int* pair_of_slot, const int* n_tiles,
                                const int* tile_expert, const int* tile_row0, int max_tiles, int top, int N, int K, int gated,
-                               float limit, float alpha, float up_offset, void* stream) {
+                               float limit, float alpha, float up_offset, int act, void* stream) {
     if (max_tiles <= 0) return 0;
     if (N <= 0 || K <= 0 || (gated && (N & 1))) return fail("moe_stream: N=%d K=%d", N, K);
     const int elem = x_dtype == EMBER_F32 ? 4 : 2;
     if (((size_t)K * elem) % 16 || ((size_t)ld_x * elem) % 16) return fail("moe_stream: rows of %d elements are no multiple of 16 bytes", K);
     const size_t smem = (size_t)MS_ROWS * K * elem;
     if (smem > 200 * 1024) return fail("moe_stream: %d rows of %d do not fit in shared memory", MS_ROWS, K);
-    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset};
+    MoeGemmArgs p{x, ld_x, w, w_expert, out, ld_o, offsets, pair_of_slot, n_tiles, tile_expert, tile_row0, top, N, K, limit, alpha, up_offset, act};
     cudaStream_t st = (cudaStream_t)stream;
     const int key = x_dtype * 100 + w_dtype * 10 + out_dtype;       // F32 = 0, BF16 = 1
     static int tc_on = -1;
@@ -591,6 +662,7 @@ EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void*
         dim3 tgrid(max_tiles, (N + MT_WARPS * 16 - 1) / (MT_WARPS * 16));
         if (gated && out_dtype == EMBER_BF16) launch_kernel(moe_stream_tc_kernel<__nv_bfloat16, true>, tgrid, MT_WARPS * 32, 0, st, p);
         else if (!gated && out_dtype == EMBER_F32) launch_kernel(moe_stream_tc_kernel<float, false>, tgrid, MT_WARPS * 32, 0, st, p);
+        else if (!gated && out_dtype == EMBER_BF16) launch_kernel(moe_stream_tc_kernel<__nv_bfloat16, false>, tgrid, MT_WARPS * 32, 0, st, p);
         else return fail("moe_stream: unsupported dtypes %d", key);
         return check_launch("moe_stream_tc");
     }
@@ -609,6 +681,7 @@ EMBER_API int ember_moe_stream(const void* x, int x_dtype, int ld_x, const void*
     } else {
         if (key == 0) return run(moe_stream_kernel<float, float, false>);
         if (key == 110) return run(moe_stream_kernel<__nv_bfloat16, float, false>);
+        if (key == 111) return run(moe_stream_kernel<__nv_bfloat16, __nv_bfloat16, false>);
     }
     return fail("moe_stream: unsupported dtypes %d", key);
 }
@@ -621,20 +694,36 @@ EMBER_API int ember_moe_gather(const void* x, const int* pair_of_slot, int n_pai
 }
 
 EMBER_API int ember_moe_activation(const float* gu, void* act, int out_dtype, long long n, float limit, float alpha, float up_offset,
-                                   void* stream) {
+                                   const float* bias, int ff, void* stream) {
     if (n <= 0) return 0;
+    if (bias && ff <= 0) return fail("moe_activation: biases for rows of %d", ff);
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (out_dtype == EMBER_F32) launch_kernel(moe_activation_kernel<float>, blocks, 256, 0, st, (const float2*)gu, (float*)act, (size_t)n, limit, alpha, up_offset);
+    if (out_dtype == EMBER_F32)
+        launch_kernel(moe_activation_kernel<float>, blocks, 256, 0, st, (const float2*)gu, (float*)act, (size_t)n, limit, alpha, up_offset, (const float2*)bias, ff);
     else if (out_dtype == EMBER_BF16)
-        launch_kernel(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const float2*)gu, (__nv_bfloat16*)act, (size_t)n, limit, alpha, up_offset);
+        launch_kernel(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const float2*)gu, (__nv_bfloat16*)act, (size_t)n, limit, alpha, up_offset,
+                      (const float2*)bias, ff);
     else return fail("moe_activation: unsupported dtype %d", out_dtype);
     return check_launch("moe_activation");
 }
 
+EMBER_API int ember_moe_square_relu(const float* x, void* act, int out_dtype, long long n, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (out_dtype == EMBER_F32) launch_kernel(moe_square_relu_kernel<float>, blocks, 256, 0, st, x, (float*)act, (size_t)n);
+    else if (out_dtype == EMBER_BF16) launch_kernel(moe_square_relu_kernel<__nv_bfloat16>, blocks, 256, 0, st, x, (__nv_bfloat16*)act, (size_t)n);
+    else return fail("moe_square_relu: unsupported dtype %d", out_dtype);
+    return check_launch("moe_square_relu");
+}
+
 EMBER_API int ember_moe_combine(const float* y, const float* wgt, const int* slot_of_pair, int T, int top, float* out, int accumulate,
-                                int hidden, void* stream) {
+                                int hidden, const int* sel, int experts, const void* same, int same_dtype, void* stream) {
     if (T <= 0) return 0;
-    launch_kernel(moe_combine_kernel, T, 256, 0, (cudaStream_t)stream, y, wgt, slot_of_pair, top, out, accumulate, hidden);
+    if (sel && (!same || (same_dtype != EMBER_F32 && same_dtype != EMBER_BF16))) return fail("moe_combine: identity experts need the tokens' input rows");
+    launch_kernel(moe_combine_kernel, T, 256, 0, (cudaStream_t)stream, y, wgt, slot_of_pair, top, out, accumulate, hidden, sel, experts,
+                  (const float*)(sel && same_dtype == EMBER_F32 ? same : nullptr),
+                  (const __nv_bfloat16*)(sel && same_dtype == EMBER_BF16 ? same : nullptr));
     return check_launch("moe_combine");
 }

@@ -2,6 +2,10 @@
 //   layer_norm        out[r] = (x - mean) / sqrt(var + eps) * w + b      (var = mean of squared deviations)
 //   gated_norm_add    residual[r] += norm(y[r] * sigmoid(gate_logits[r])) for a layer norm or an RMS norm; the new
 //                     residual row can also be left rounded to bfloat16 (for a sublayer that reads the stream itself)
+//   scaled_add_norm   residual[r] = norm(alpha * residual[r] + y[r] + bias): the norm *after* the sum (a post-norm layer), in place,
+//                     with the same optional bfloat16 copy of the new rows
+//   pair_norm_sum     out[r] (+)= wa * a[r] / rms(a[r]) + wb * b[r] / rms(b[r]): two branches, each RMS-normed over the row
+//   add_row_bias      y[r] += bias
 //   round_rows        out = bfloat16(x)
 //   group_norm_gate   a token's row cut into groups, each divided by its own root mean square, times a weight,
 //                     with a gate before (silu) or after (sigmoid or silu) the norm
@@ -79,6 +83,69 @@ gated_norm_add_kernel(const float* __restrict__ y, const float* __restrict__ gat
         residual[base + i] = r;
         if (rounded) rounded[base + i] = __float2bfloat16_rn(r);      // what the next sublayer's products read
     }
+}
+
+// ------------------------------------------------------------------------------- norm after the residual sum
+// residual[r] = norm(alpha * residual[r] + y[r] + y_bias) * w + b: the stream is scaled, the sublayer's result (and
+// the bias its last product left out, if any) added, and the sum normed in place.
+template <bool CENTRED>
+__global__ void __launch_bounds__(ROW_THREADS)
+scaled_add_norm_kernel(const float* __restrict__ y, const float* __restrict__ y_bias, float alpha, const float* __restrict__ w,
+                       const float* __restrict__ b, float eps, float* __restrict__ residual, __nv_bfloat16* __restrict__ rounded,
+                       int H) {
+    extern __shared__ float row[];          // H floats: the sum
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float s = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float v = fmaf(alpha, residual[base + i], y[base + i] + (y_bias ? y_bias[i] : 0.0f));
+        row[i] = v;
+        s += v;
+    }
+    float mean = 0.0f;
+    if (CENTRED) mean = block_sum(s, scratch) / (float)H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float d = row[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float r = (row[i] - mean) * rstd * w[i] + (b ? b[i] : 0.0f);
+        residual[base + i] = r;
+        if (rounded) rounded[base + i] = __float2bfloat16_rn(r);
+    }
+}
+
+// out[r] (+)= wa * a[r] / rms(a[r]) + wb * b[r] / rms(b[r]); each root mean square over the whole row, eps inside the root.
+__global__ void __launch_bounds__(ROW_THREADS)
+pair_norm_sum_kernel(const float* __restrict__ a, const float* __restrict__ wa, const float* __restrict__ b,
+                     const float* __restrict__ wb, float eps, float* __restrict__ out, int accumulate, int H) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * H;
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float x = a[base + i], z = b[base + i];
+        sa = fmaf(x, x, sa);
+        sb = fmaf(z, z, sb);
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, scratch) / (float)H + eps);
+    const float rb = 1.0f / sqrtf(block_sum(sb, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += ROW_THREADS) {
+        const float v = fmaf(a[base + i] * ra, wa[i], b[base + i] * rb * wb[i]);
+        out[base + i] = accumulate ? out[base + i] + v : v;
+    }
+}
+
+__global__ void add_row_bias_kernel(float* __restrict__ y, const float* __restrict__ bias, size_t n, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] += bias[i % H];
 }
 
 // ---------------------------------------------------------------------------------- per-group RMS norm with gate
@@ -367,6 +434,37 @@ EMBER_API int ember_gated_norm_add(const float* y, const float* gate, const floa
     if (centred) launch_kernel(gated_norm_add_kernel<true>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
     else launch_kernel(gated_norm_add_kernel<false>, n_rows, ROW_THREADS, smem, st, y, gate, gate_bias, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
     return check_launch("gated_norm_add");
+}
+
+EMBER_API int ember_scaled_add_norm(const float* y, const float* y_bias, float alpha, const float* w, const float* b, float eps,
+                                    int centred, float* residual, void* rounded, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || (size_t)H * 4 > 200 * 1024) return fail("scaled_add_norm: width %d is not taken", H);
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(scaled_add_norm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(scaled_add_norm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (centred) launch_kernel(scaled_add_norm_kernel<true>, n_rows, ROW_THREADS, smem, st, y, y_bias, alpha, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
+    else launch_kernel(scaled_add_norm_kernel<false>, n_rows, ROW_THREADS, smem, st, y, y_bias, alpha, w, b, eps, residual, (__nv_bfloat16*)rounded, H);
+    return check_launch("scaled_add_norm");
+}
+
+EMBER_API int ember_pair_norm_sum(const float* a, const float* wa, const float* b, const float* wb, float eps, float* out,
+                                  int accumulate, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return fail("pair_norm_sum: bad width %d", H);
+    launch_kernel(pair_norm_sum_kernel, n_rows, ROW_THREADS, 0, (cudaStream_t)stream, a, wa, b, wb, eps, out, accumulate, H);
+    return check_launch("pair_norm_sum");
+}
+
+EMBER_API int ember_add_row_bias(float* y, const float* bias, int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return fail("add_row_bias: bad width %d", H);
+    const size_t n = (size_t)n_rows * H;
+    launch_kernel(add_row_bias_kernel, (unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream, y, bias, n, H);
+    return check_launch("add_row_bias");
 }
 
 EMBER_API int ember_group_norm_gate(const float* x, int ldx, const float* gate, int ldg, const float* w, int w_stride,

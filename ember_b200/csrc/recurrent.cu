@@ -20,12 +20,12 @@ __device__ __forceinline__ float softplusf_(float x) { return x > 20.0f ? x : lo
 __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.0f) - log1pf(expf(-fabsf(x))); }
 
 // ------------------------------------------------------------------------------- short causal convolution + silu
-// out[t, c] = silu(bias[c] + sum_j taps[c, j] * in(t - (n - 1 - j), c)); inputs before the run come from the
+// out[t, c] = silu(bias[c] + sum_j taps[c, j] * in(t - (n - 1 - j), c)) (or, silu = 0, the sum itself); inputs before the run come from the
 // request's carried inputs carry[slot][j][c] (j = 0 the oldest of n - 1), zeros for a new request.
 __global__ void conv_silu_kernel(const float* __restrict__ x, int ldx, int c0, const float* __restrict__ taps,
                                  const float* __restrict__ bias, int n, const float* __restrict__ carry, long long carry_stride,
                                  const int* __restrict__ seq_of, const int* __restrict__ query_start,
-                                 const int* __restrict__ slots, float* __restrict__ out, int C) {
+                                 const int* __restrict__ slots, float* __restrict__ out, int C, int silu) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -38,7 +38,7 @@ __global__ void conv_silu_kernel(const float* __restrict__ x, int ldx, int c0, c
         const float v = src >= first ? x[(size_t)src * ldx + c0 + c] : cs[(size_t)(n - 1 + src - first) * C + c];
         acc = fmaf(taps[(size_t)c * n + j], v, acc);
     }
-    out[(size_t)t * C + c] = acc / (1.0f + expf(-acc));
+    out[(size_t)t * C + c] = silu ? acc / (1.0f + expf(-acc)) : acc;
 }
 
 // After the convolution: the request's last n - 1 inputs (from the run, or shifted down from what was carried).
@@ -170,14 +170,15 @@ __device__ __forceinline__ void store_tile(const float* tile, float* __restrict_
 struct DeltaArgs {
     const float* conv; int ld_conv;        // [T, G D | G D | H V] after convolution and silu
     const float* beta; int ld_beta;        // [T, H] logits
-    const float* a; int ld_a;              // [T, H D] decay logits (before the bias)
-    const float* dt_bias;                  // [H D]
+    const float* a; int ld_a;              // [T, H D] decay logits (before the bias); a_head: [T, H], one decay per head
+    const float* dt_bias;                  // [H D] (a_head: [H])
     const float* A_log;                    // [H]
     float* state; long long state_stride;  // [slot][H][D][V]
     float* out;                            // [T, H V]
     const int* query_start; const int* slots;
     int H, G, D, V;
     float key_eps;
+    int a_head;
 };
 
 __global__ void delta_scan_kernel(DeltaArgs p) {
@@ -205,7 +206,8 @@ __global__ void delta_scan_kernel(DeltaArgs p) {
             const float kr = row[off_k + kv * D + i], qr = row[kv * D + i];
             kb[i] = kr; qb[i] = qr;
             sk = fmaf(kr, kr, sk); sq = fmaf(qr, qr, sq);
-            gb[i] = expf(-rate * softplusf_(p.a[(size_t)t * p.ld_a + h * D + i] + p.dt_bias[h * D + i]));
+            const int ai = p.a_head ? h : h * D + i;
+            gb[i] = expf(-rate * softplusf_(p.a[(size_t)t * p.ld_a + ai] + p.dt_bias[ai]));
         }
         sk = warp_sum(sk); sq = warp_sum(sq);
         if (lane == 0) { red[b * 64 + warp] = sk; red[b * 64 + 32 + warp] = sq; }
@@ -561,6 +563,7 @@ struct ScanArgs {
     float* gates;                          // matrix memory: [T, H, 4]
     float decay_power;                     // gated linear attention: 1 / tau
     const float* bonus;                    // time mixing: u [H D] (its w0 is dt_bias)
+    int a_head;                            // delta: one decay logit (and bias) per head instead of per head and key channel
 };
 
 template <int N>
@@ -614,7 +617,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                 if (i < D) {
                     f0[w][m] = row[off0 + i];
                     f1[w][m] = row[off1 + i];
-                    if (MODE == 0 || MODE == 3 || MODE == 4) f2[w][m] = p.a[(size_t)t * p.ld_a + h * D + i];
+                    if (MODE == 0 || MODE == 3 || MODE == 4) f2[w][m] = p.a[(size_t)t * p.ld_a + ((MODE == 0 && p.a_head) ? h : h * D + i)];
                 }
             }
             const int c = col0 + lane;
@@ -643,7 +646,7 @@ __global__ void __launch_bounds__(32 * RG, CT == 1 ? 3 : 1) scan_chunks_kernel(S
                         s0 = fmaf(f1[w][m] * p.bonus[h * D + i], f0[w][m], s0);          // r . (u k)
                     }
                     if (MODE == 0) {
-                        tok[2 * VS + vi] = expf(-rate * softplusf_(f2[w][m] + p.dt_bias[h * D + i]));
+                        tok[2 * VS + vi] = expf(-rate * softplusf_(f2[w][m] + p.dt_bias[p.a_head ? h : h * D + i]));
                         s0 = fmaf(f0[w][m], f0[w][m], s0); s1 = fmaf(f1[w][m], f1[w][m], s1); s01 = fmaf(f0[w][m], f1[w][m], s01);
                     }
                 }
@@ -838,14 +841,14 @@ using namespace ember;
 
 EMBER_API int ember_conv_silu(const float* x, int ldx, int c0, const float* taps, const float* bias, int n, float* carry,
                               long long carry_stride, const int* seq_of, const int* query_start, const int* slots, float* out,
-                              int T, int S, int C, void* stream) {
+                              int T, int S, int C, int silu, void* stream) {
     if (T <= 0 || S <= 0) return 0;
     if (C <= 0 || n < 1 || n > 64 || ldx < c0 + C) return fail("conv_silu: %d channels from column %d in rows of %d, %d taps", C, c0, ldx, n);
     if (T > 65535 || S > 65535) return fail("conv_silu: %d tokens in %d runs are too many for one launch", T, S);
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned bx = (unsigned)((C + 127) / 128);
     launch_kernel(conv_silu_kernel, dim3(bx, T), 128, 0, st, x, ldx, c0, taps, bias, n, (const float*)carry, carry_stride, seq_of,
-                  query_start, slots, out, C);
+                  query_start, slots, out, C, silu);
     if (n > 1)
         launch_kernel(conv_carry_kernel, dim3(bx, S), 128, 0, st, x, ldx, c0, n, carry, carry_stride, query_start, slots, C);
     return check_launch("conv_silu");
@@ -854,19 +857,19 @@ EMBER_API int ember_conv_silu(const float* x, int ldx, int c0, const float* taps
 EMBER_API int ember_delta_scan(const float* conv, int ld_conv, const float* beta, int ld_beta, const float* a, int ld_a,
                                const float* dt_bias, const float* A_log, float* state, long long state_stride, float* out,
                                const int* query_start, const int* slots, int T, int S, int H, int G, int D, int V, float key_eps,
-                               void* stream) {
+                               int a_head, void* stream) {
     if (S <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || V <= 0) return fail("delta_scan: %d/%d heads of %d x %d", H, G, D, V);
     if (S > 65535 || H > 65535) return fail("delta_scan: too many runs or heads for one launch");
     size_t smem;
     const int VT = pick_columns(D, V, 6 * D + 128, &smem);
     if (allow_smem(delta_scan_kernel, smem, "delta_scan")) return 1;
-    DeltaArgs p{conv, ld_conv, beta, ld_beta, a, ld_a, dt_bias, A_log, state, state_stride, out, query_start, slots, H, G, D, V, key_eps};
+    DeltaArgs p{conv, ld_conv, beta, ld_beta, a, ld_a, dt_bias, A_log, state, state_stride, out, query_start, slots, H, G, D, V, key_eps, a_head};
     if (rows_per_thread(D) && regs_kernels_on()) {
         ScanArgs q{};
         q.state = state; q.state_stride = state_stride; q.out = out; q.query_start = query_start; q.slots = slots;
         q.H = H; q.G = G; q.D = D; q.V = V; q.x = conv; q.ld_x = ld_conv; q.b = beta; q.ld_b = ld_beta; q.a = a; q.ld_a = ld_a;
-        q.dt_bias = dt_bias; q.A_log = A_log; q.key_eps = key_eps;
+        q.dt_bias = dt_bias; q.A_log = A_log; q.key_eps = key_eps; q.a_head = a_head;
         if (launch_scan<0>(q, S, V, T == S, (cudaStream_t)stream)) return 1;
         return check_launch("delta_scan");
     }

@@ -86,6 +86,105 @@ __global__ void __launch_bounds__(256) whole_norm_store_kernel(WholeNormArgs p) 
     }
 }
 
+// --------------------------------------------------------------- q/k/v of a token: norm, rotation, temperature
+// The general form of whole_norm_store.  norm_mode 0: none; 1: one RMS norm over the whole query projection and one
+// over the whole key projection (weights of that size); 2: an RMS norm per head (weights of D, shared by the heads).
+// Then the first `rotary` elements of every query and key head turn (element i with i + rotary / 2) by the angle
+// position * inv_freq[i], and the query is multiplied by 1 + qt_coef * ln(floor((position + 1) / qt_every) + 1)
+// (qt_every 0: not).  Queries out, keys and values into the token's page.
+struct HeadPrepareArgs {
+    const float* qkv; int ld;          // [T, q | k | v] fp32
+    const float* bias;                 // [q | k | v] or null
+    int norm_mode; const float* q_w; const float* k_w; float eps;
+    const float* inv_freq; int rotary;
+    float qt_coef; int qt_every;
+    int H, G, D, DV;
+    const int* positions; const int* seq_of; const int* block_table;
+    int max_blocks, page, num_pages;
+    void* q_out; void* k_pool; void* v_pool;
+    int write_kv;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) head_prepare_store_kernel(HeadPrepareArgs p) {
+    extern __shared__ float factor[];          // per-head norm factors: H for the queries, then G for the keys
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int D = p.D, QN = p.H * D, KN = p.G * D, VN = p.G * p.DV;
+    const float* row = p.qkv + (size_t)t * p.ld;
+    const float* b = p.bias;
+    const bool kv = p.write_kv != 0;
+    auto val = [&](int i) { return row[i] + (b ? b[i] : 0.0f); };
+    float rq = 1.0f, rk = 1.0f;
+    if (p.norm_mode == 1) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < QN; i += blockDim.x) { const float v = val(i); ss = fmaf(v, v, ss); }
+        rq = 1.0f / sqrtf(block_sum(ss, scratch) / (float)QN + p.eps);
+        if (kv) {
+            ss = 0.0f;
+            for (int i = threadIdx.x; i < KN; i += blockDim.x) { const float v = val(QN + i); ss = fmaf(v, v, ss); }
+            rk = 1.0f / sqrtf(block_sum(ss, scratch) / (float)KN + p.eps);
+        }
+    } else if (p.norm_mode == 2) {
+        const int heads = p.H + (kv ? p.G : 0);
+        for (int h = warp; h < heads; h += nw) {
+            float ss = 0.0f;
+            for (int d = lane; d < D; d += 32) { const float v = val(h * D + d); ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) factor[h] = 1.0f / sqrtf(ss / (float)D + p.eps);
+        }
+        __syncthreads();
+    }
+    const int pos = p.positions[t];
+    const int half = p.rotary / 2;
+    // element i of [q | k] (i < QN: a query element), normed and weighed
+    auto normed = [&](int i) {
+        const bool isq = i < QN;
+        const int j = isq ? i : i - QN;
+        float v = val(i);
+        if (p.norm_mode == 1) v *= (isq ? rq : rk) * (isq ? p.q_w[j] : p.k_w[j]);
+        else if (p.norm_mode == 2) v *= factor[i / D] * (isq ? p.q_w[j % D] : p.k_w[j % D]);
+        return v;
+    };
+    auto turned = [&](int i) {
+        const int d = i % D;
+        float v = normed(i);
+        if (d < p.rotary) {
+            const bool low = d < half;
+            const float other = normed(low ? i + half : i - half);
+            float sn, cs;
+            sincosf((float)pos * p.inv_freq[low ? d : d - half], &sn, &cs);
+            v = low ? v * cs - other * sn : v * cs + other * sn;
+        }
+        return v;
+    };
+    float temp = 1.0f;
+    if (p.qt_every > 0) temp = 1.0f + p.qt_coef * logf((float)((pos + 1) / p.qt_every) + 1.0f);
+    T* qo = (T*)p.q_out + (size_t)t * QN;
+    for (int i = threadIdx.x; i < QN; i += blockDim.x) qo[i] = from_float<T>(turned(i) * temp);
+    if (!kv) return;
+    const int seq = p.seq_of[t];
+    const int blk = p.block_table[(size_t)seq * p.max_blocks + pos / p.page];
+    if (blk < 0 || blk >= p.num_pages) {
+        if (threadIdx.x == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+        return;
+    }
+    const int in_page = pos % p.page;
+    T* kp = (T*)p.k_pool;
+    T* vp = (T*)p.v_pool;
+    for (int i = threadIdx.x; i < KN; i += blockDim.x) {
+        const int g = i / D, d = i - g * D;
+        kp[(((size_t)blk * p.G + g) * p.page + in_page) * D + d] = from_float<T>(turned(QN + i));
+    }
+    for (int i = threadIdx.x; i < VN; i += blockDim.x) {
+        const int g = i / p.DV, d = i - g * p.DV;
+        vp[(((size_t)blk * p.G + g) * p.page + in_page) * p.DV + d] = from_float<T>(val(QN + KN + i));
+    }
+}
+
 // ------------------------------------------------------------------------------------- latents of a token
 struct LatentArgs {
     const float* a; int ld;            // [T, ...] fp32: the fused down-projections
@@ -268,7 +367,25 @@ struct SinkAttnParams {
     float scale;
     int n_splits, split_keys;
     int* err;
+    int chunk;            // > 0: position i sees j only if i / chunk == j / chunk (chunks counted from position 0 of the sequence)
+    float softcap;        // > 0: score <- softcap * tanh(score / softcap), after the scale
+    const float* head_gate; int ld_gate;   // [T, ld_gate] logits, one per head: the head's output is multiplied by its sigmoid; or null
 };
+
+// First key a tile starting at position pos0 can see, and whether key `key` is visible from position qpos.
+__device__ __forceinline__ int first_visible(const SinkAttnParams& p, int pos0) {
+    int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, pos0 - pos0 % p.chunk);
+    return lo;
+}
+__device__ __forceinline__ bool key_visible(const SinkAttnParams& p, int key, int qpos) {
+    return key <= qpos && (p.window <= 0 || qpos - key < p.window || key < p.keep_first) &&
+           (p.chunk <= 0 || key >= qpos - qpos % p.chunk);
+}
+__device__ __forceinline__ float capped_score(const SinkAttnParams& p, float dot) {
+    const float s = dot * p.scale;
+    return p.softcap > 0.0f ? p.softcap * tanhf(s / p.softcap) : s;
+}
 
 template <typename T, typename TO, int NC>
 __global__ void __launch_bounds__(SA_WARPS * 32)
@@ -303,7 +420,7 @@ sink_attention_kernel(SinkAttnParams p) {
     }
 
     // visible keys of the tile: [0, kept) and [lo, hi); with a split, their part inside the split
-    int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int lo = first_visible(p, pos0);
     int hi = pos0 + nq;
     int kept = p.window > 0 ? min(p.keep_first, lo) : 0;
     int s_lo = 0, s_hi = hi;
@@ -389,9 +506,8 @@ sink_attention_kernel(SinkAttnParams p) {
                 pj[i] = 0.0f;
                 if (r >= rows) continue;  // uniform per warp
                 const int qpos = pos0 + r / nh;
-                const bool visible = key >= a && key < b && key <= qpos &&
-                                     (p.window <= 0 || qpos - key < p.window || key < p.keep_first);
-                const float sv = visible ? sc[i] * p.scale : -INFINITY;
+                const bool visible = key >= a && key < b && key_visible(p, key, qpos);
+                const float sv = visible ? capped_score(p, sc[i]) : -INFINITY;
                 const float m_new = fmaxf(m[i], warp_max(sv));
                 if (m_new == -INFINITY) continue;  // nothing visible so far (uniform per warp)
                 const float corr = expf(m[i] - m_new);
@@ -438,7 +554,8 @@ sink_attention_kernel(SinkAttnParams p) {
                 corr = expf(m[i] - mm);
                 ll = l[i] * corr + expf(sk - mm);
             }
-            const float inv = ll > 0.0f ? corr / ll : 0.0f;
+            float inv = ll > 0.0f ? corr / ll : 0.0f;
+            if (p.head_gate) inv *= sigmoidf_(p.head_gate[(size_t)(row0 + qi) * p.ld_gate + head]);
             TO* o = (TO*)p.out + th * DV;
 #pragma unroll
             for (int c = 0; c < NC; c++) {
@@ -464,7 +581,8 @@ sink_attention_kernel(SinkAttnParams p) {
 // Merges the splits of one (token, head) in ascending order; the sink joins here.
 template <typename TO>
 __global__ void sink_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const float* __restrict__ sink, TO* __restrict__ out, int n_splits, int DV, int H) {
+                                    const float* __restrict__ sink, TO* __restrict__ out, int n_splits, int DV, int H,
+                                    const float* __restrict__ head_gate, int ld_gate) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t th = blockIdx.x;
@@ -476,7 +594,8 @@ __global__ void sink_combine_kernel(const float* __restrict__ part_o, const floa
         const float ms = ml[2 * s];
         if (ms != -INFINITY) L += ml[2 * s + 1] * expf(ms - M);
     }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    if (head_gate) inv *= sigmoidf_(head_gate[(th / H) * (size_t)ld_gate + th % H]);
     for (int d = threadIdx.x; d < DV; d += blockDim.x) {
         float o = 0.0f;
         for (int s = 0; s < n_splits; s++) {
@@ -513,7 +632,7 @@ int launch_sink_attention(const SinkAttnParams& p, int n_tiles, int T_tokens, cu
     if (rc) return rc;
     if (p.n_splits > 1) {
         launch_kernel(sink_combine_kernel<TO>, (unsigned)((size_t)T_tokens * p.H), DV >= 128 ? 128 : 64, 0, st,
-                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, DV, p.H);
+                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, DV, p.H, p.head_gate, p.ld_gate);
         return check_launch("sink_combine");
     }
     return 0;
@@ -651,7 +770,7 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
         *reinterpret_cast<uint4*>(Qs + r * DP + c * 8) = v;
     }
 
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = first_visible(p, pos0);
     const int hi = pos0 + nq;
     const int kept = p.window > 0 ? min(p.keep_first, lo) : 0;
     const int rA = wr * 16 + g, rB = rA + 8;                   // the thread's two rows
@@ -753,10 +872,10 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
                 for (int e = 0; e < 2; e++) {
                     const int key = k0 + nt * 8 + 2 * t + e;
                     const bool in = key >= a && key < b;
-                    const bool vA = liveA && in && key <= qposA && (p.window <= 0 || qposA - key < p.window || key < p.keep_first);
-                    const bool vB = liveB && in && key <= qposB && (p.window <= 0 || qposB - key < p.window || key < p.keep_first);
-                    sc[nt][e] = vA ? sc[nt][e] * p.scale : -INFINITY;
-                    sc[nt][2 + e] = vB ? sc[nt][2 + e] * p.scale : -INFINITY;
+                    const bool vA = liveA && in && key_visible(p, key, qposA);
+                    const bool vB = liveB && in && key_visible(p, key, qposB);
+                    sc[nt][e] = vA ? capped_score(p, sc[nt][e]) : -INFINITY;
+                    sc[nt][2 + e] = vB ? capped_score(p, sc[nt][2 + e]) : -INFINITY;
                     tmA = fmaxf(tmA, sc[nt][e]);
                     tmB = fmaxf(tmB, sc[nt][2 + e]);
                 }
@@ -841,6 +960,10 @@ __global__ void __launch_bounds__(256, 1) shared_row_attention_tc_kernel(SinkAtt
         mm = mB; ll = lB; corr = 1.0f;
         if (p.sink) { const float sk = p.sink[hB]; mm = fmaxf(mB, sk); corr = mB == -INFINITY ? 0.0f : expf(mB - mm); ll = lB * corr + expf(sk - mm); }
         invB = ll > 0.0f ? corr / ll : 0.0f;
+        if (p.head_gate) {
+            if (liveA) invA *= sigmoidf_(p.head_gate[(size_t)(row0 + rA / nh) * p.ld_gate + hA]);
+            if (liveB) invB *= sigmoidf_(p.head_gate[(size_t)(row0 + rB / nh) * p.ld_gate + hB]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < NTO; i++) {
@@ -878,7 +1001,7 @@ int launch_shared_row_tc(const SinkAttnParams& p, int n_tiles, int T_tokens, cud
     if (rc) return rc;
     if (p.n_splits > 1) {
         launch_kernel(sink_combine_kernel<TO>, (unsigned)((size_t)T_tokens * p.H), p.DV >= 128 ? 128 : 64, 0, st,
-                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, p.DV, p.H);
+                      (const float*)p.part_o, (const float*)p.part_ml, p.sink, (TO*)p.out, p.n_splits, p.DV, p.H, p.head_gate, p.ld_gate);
         return check_launch("sink_combine");
     }
     return 0;
@@ -903,6 +1026,27 @@ EMBER_API int ember_whole_norm_store(const float* qkv, int ld, const float* bias
     else if (dtype == EMBER_BF16) launch_kernel(whole_norm_store_kernel<__nv_bfloat16>, T, 256, 0, st, p);
     else return fail("whole_norm_store: unsupported dtype %d", dtype);
     return check_launch("whole_norm_store");
+}
+
+EMBER_API int ember_head_prepare_store(const float* qkv, int ld, const float* bias, int norm_mode, const float* q_w, const float* k_w,
+                                       float eps, const float* inv_freq, int rotary, float qt_coef, int qt_every, int T_tokens, int H,
+                                       int G, int D, int DV, const int* positions, const int* seq_of, const int* block_table,
+                                       int max_blocks, int page, int num_pages, void* q_out, void* k_pool, void* v_pool, int dtype,
+                                       int write_kv, int* err, void* stream) {
+    if (T_tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || D <= 0 || DV <= 0 || ld < H * D + G * (D + DV)) return fail("head_prepare_store: %d/%d heads of %d / %d in rows of %d", H, G, D, DV, ld);
+    if (norm_mode < 0 || norm_mode > 2 || (norm_mode && (!q_w || !k_w))) return fail("head_prepare_store: norm mode %d", norm_mode);
+    if (rotary < 0 || rotary > D || (rotary & 1) || (rotary && !inv_freq)) return fail("head_prepare_store: %d rotated elements of %d", rotary, D);
+    if (qt_every < 0 || page <= 0 || max_blocks <= 0 || num_pages <= 0) return fail("head_prepare_store: bad geometry");
+    HeadPrepareArgs p{qkv, ld, bias, norm_mode, q_w, k_w, eps, inv_freq, rotary, qt_coef, qt_every, H, G, D, DV, positions, seq_of,
+                      block_table, max_blocks, page, num_pages, q_out, k_pool, v_pool, write_kv, err};
+    const size_t smem = (size_t)(H + G) * sizeof(float);
+    if (smem > 40 * 1024) return fail("head_prepare_store: %d heads are too many", H + G);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32) launch_kernel(head_prepare_store_kernel<float>, T_tokens, 256, smem, st, p);
+    else if (dtype == EMBER_BF16) launch_kernel(head_prepare_store_kernel<__nv_bfloat16>, T_tokens, 256, smem, st, p);
+    else return fail("head_prepare_store: unsupported dtype %d", dtype);
+    return check_launch("head_prepare_store");
 }
 
 EMBER_API int ember_latent_prepare(const float* a, int ld, int q_col, int q_rank, int c_col, int kv_rank, int rot_dim,
@@ -969,7 +1113,7 @@ EMBER_API int ember_sink_attention(const void* q, const void* k_pool, const void
                                    int T_tokens, int H, int G, int D, int DV, const int* tiles, int n_tiles, int tile_q,
                                    const int* block_table, int max_blocks, int page, int num_pages, int window,
                                    int keep_first, const float* sink, float scale, int n_splits, int split_keys,
-                                   float* part_o, float* part_ml, int* err, void* stream) {
+                                   float* part_o, float* part_ml, int* err, int key_chunk, float softcap, const float* head_gate, int ld_gate, void* stream) {
     if (n_tiles <= 0 || T_tokens <= 0) return 0;
     if (D <= 0 || DV <= 0 || DV > 512 || (!v_pool && DV > D)) return fail("sink_attention: heads of %d / %d are not taken", D, DV);
     if (H <= 0 || G <= 0 || H % G) return fail("sink_attention: %d heads do not divide into %d groups", H, G);
@@ -985,6 +1129,8 @@ EMBER_API int ember_sink_attention(const void* q, const void* k_pool, const void
     p.tiles = tiles; p.block_table = block_table; p.sink = sink; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
     p.H = H; p.G = G; p.D = D; p.DV = DV; p.head_chunk = chunk; p.window = window; p.keep_first = keep_first; p.scale = scale;
     p.n_splits = n_splits; p.split_keys = split_keys; p.err = err;
+    if (key_chunk < 0 || softcap < 0.0f || (head_gate && ld_gate < H)) return fail("sink_attention: chunk %d, score cap %g, gate rows of %d", key_chunk, softcap, ld_gate);
+    p.chunk = key_chunk; p.softcap = softcap; p.head_gate = head_gate; p.ld_gate = ld_gate;
     cudaStream_t st = (cudaStream_t)stream;
     if (dtype == EMBER_F32) return launch_sink_attention<float, float>(p, n_tiles, T_tokens, st);
     if (dtype == EMBER_BF16)
@@ -1001,7 +1147,7 @@ EMBER_API int ember_shared_row_attention_tc_head_chunk(int group) { return group
 EMBER_API int ember_shared_row_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out, int out_f32, int T_tokens, int H, int G, int D,
                                             int DV, const int* tiles, int n_tiles, int tile_q, const int* block_table, int max_blocks,
                                             int page, int num_pages, int window, int keep_first, const float* sink, float scale,
-                                            int n_splits, int split_keys, float* part_o, float* part_ml, int* err, void* stream) {
+                                            int n_splits, int split_keys, float* part_o, float* part_ml, int* err, int key_chunk, float softcap, const float* head_gate, int ld_gate, void* stream) {
     if (n_tiles <= 0 || T_tokens <= 0) return 0;
     if (D <= 0 || DV <= 0 || (D & 15) || (DV & 15) || (!v_pool && DV > D) || DV > 512) return fail("shared_row_attention_tc: rows of %d / %d are not taken", D, DV);
     if (H <= 0 || G <= 0 || H % G) return fail("shared_row_attention_tc: %d heads do not divide into %d groups", H, G);
@@ -1016,6 +1162,8 @@ EMBER_API int ember_shared_row_attention_tc(const void* q, const void* k_pool, c
     p.tiles = tiles; p.block_table = block_table; p.sink = sink; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
     p.H = H; p.G = G; p.D = D; p.DV = DV; p.head_chunk = chunk; p.window = window; p.keep_first = keep_first; p.scale = scale;
     p.n_splits = n_splits; p.split_keys = split_keys; p.err = err;
+    if (key_chunk < 0 || softcap < 0.0f || (head_gate && ld_gate < H)) return fail("sink_attention: chunk %d, score cap %g, gate rows of %d", key_chunk, softcap, ld_gate);
+    p.chunk = key_chunk; p.softcap = softcap; p.head_gate = head_gate; p.ld_gate = ld_gate;
     cudaStream_t st = (cudaStream_t)stream;
     return out_f32 ? launch_shared_row_tc<float>(p, n_tiles, T_tokens, st) : launch_shared_row_tc<__nv_bfloat16>(p, n_tiles, T_tokens, st);
 }

@@ -608,6 +608,52 @@ def gated_norm_add(y: torch.Tensor, gate_logits: Optional[torch.Tensor], weight:
           _p(residual), _p(rounded), c_int(n_rows), c_int(H), _stream(stream))
 
 
+def scaled_add_norm(y: torch.Tensor, y_bias: Optional[torch.Tensor], alpha: float, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                    eps: float, centred: bool, residual: torch.Tensor, n_rows: int, rounded: Optional[torch.Tensor] = None,
+                    stream: Optional[int] = None) -> None:
+    """residual[r] = norm(alpha * residual[r] + y[r] + y_bias) in place: the norm after the residual sum, a layer norm
+    (``centred``) or an RMS norm, all fp32.  ``rounded`` (bfloat16) also receives the new rows, rounded once."""
+    for t, n in ((y, "y"), (weight, "weight"), (residual, "residual")) + (((y_bias, "y_bias"),) if y_bias is not None else ()) + \
+            (((bias, "bias"),) if bias is not None else ()):
+        _check(t, n, torch.float32)
+    H = residual.shape[-1]
+    if y.shape[-1] != H or weight.numel() != H or y.numel() < n_rows * H or residual.numel() < n_rows * H or \
+            (y_bias is not None and y_bias.numel() != H) or (bias is not None and bias.numel() != H):
+        raise KernelError(f"scaled_add_norm: rows of {H}, y {tuple(y.shape)}, weight {tuple(weight.shape)}")
+    if rounded is not None:
+        _check(rounded, "rounded", torch.bfloat16)
+        if rounded.shape[-1] != H or rounded.numel() < n_rows * H:
+            raise KernelError("scaled_add_norm: the rounded copy does not fit the rows")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_scaled_add_norm, _p(y), _p(y_bias), c_float(alpha), _p(weight), _p(bias), c_float(eps), c_int(1 if centred else 0),
+          _p(residual), _p(rounded), c_int(n_rows), c_int(H), _stream(stream))
+
+
+def pair_norm_sum(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: torch.Tensor, eps: float, out: torch.Tensor, n_rows: int,
+                  accumulate: bool = False, stream: Optional[int] = None) -> None:
+    """out[r] (+)= wa * a[r] / rms(a[r]) + wb * b[r] / rms(b[r]), each root mean square over the whole row (eps inside the
+    root); all fp32."""
+    for t, n in ((a, "a"), (wa, "wa"), (b, "b"), (wb, "wb"), (out, "out")):
+        _check(t, n, torch.float32)
+    H = out.shape[-1]
+    if a.shape[-1] != H or b.shape[-1] != H or wa.numel() != H or wb.numel() != H or min(a.numel(), b.numel(), out.numel()) < n_rows * H:
+        raise KernelError("pair_norm_sum: buffers do not fit the rows")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_pair_norm_sum, _p(a), _p(wa), _p(b), _p(wb), c_float(eps), _p(out), c_int(1 if accumulate else 0), c_int(n_rows),
+          c_int(H), _stream(stream))
+
+
+def add_row_bias(y: torch.Tensor, bias: torch.Tensor, n_rows: int, stream: Optional[int] = None) -> None:
+    """y[r] += bias for the first ``n_rows`` rows (fp32)."""
+    _check(y, "y", torch.float32)
+    _check(bias, "bias", torch.float32)
+    H = y.shape[-1]
+    if bias.numel() != H or y.numel() < n_rows * H:
+        raise KernelError("add_row_bias: buffers do not fit")
+    lib = _lib("norm_gate")
+    _call(lib, lib.ember_add_row_bias, _p(y), _p(bias), c_int(n_rows), c_int(H), _stream(stream))
+
+
 def round_rows(x: torch.Tensor, out: torch.Tensor, n: int, stream: Optional[int] = None) -> None:
     """out[:n] = bfloat16(x[:n]) (fp32 in): what a sublayer that reads the residual stream itself multiplies."""
     _check(x, "x", torch.float32)
@@ -770,8 +816,8 @@ def _check_runs(query_start: torch.Tensor, slots: torch.Tensor, S: int) -> None:
 
 def conv_silu(x: torch.Tensor, col: int, taps: torch.Tensor, bias: Optional[torch.Tensor], carry: torch.Tensor,
               carry_col: int, seq_of: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
-              T: int, S: int, stream: Optional[int] = None) -> None:
-    """Short causal convolution per channel + silu over the step's runs.  ``x`` fp32 [T, ld]: channels are its
+              T: int, S: int, stream: Optional[int] = None, silu: bool = True) -> None:
+    """Short causal convolution per channel + silu (``silu`` False: the convolution alone) over the step's runs.  ``x`` fp32 [T, ld]: channels are its
     columns col .. col + C; ``taps`` fp32 [C, n] (the last column meets the current token); ``carry`` fp32
     [slots, row]: a request's last n - 1 inputs live at columns carry_col .. carry_col + (n - 1) C of its row and
     are replaced by this step's."""
@@ -786,26 +832,30 @@ def conv_silu(x: torch.Tensor, col: int, taps: torch.Tensor, bias: Optional[torc
     lib = _lib("recurrent")
     _call(lib, lib.ember_conv_silu, _p(x), c_int(x.shape[1]), c_int(col), _p(taps), _p(bias), c_int(n), _off(carry, carry_col),
           c_longlong(carry.shape[1]), _p(seq_of), _p(query_start), _p(slots), _p(out), c_int(T), c_int(S), c_int(C),
-          _stream(stream))
+          c_int(1 if silu else 0), _stream(stream))
 
 
 def delta_scan(conv: torch.Tensor, beta: torch.Tensor, beta_col: int, a: torch.Tensor, a_col: int, dt_bias: torch.Tensor,
                A_log: torch.Tensor, state: torch.Tensor, out: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
-               T: int, S: int, heads: int, kv_heads: int, dim: int, vdim: int, key_eps: float, stream: Optional[int] = None) -> None:
+               T: int, S: int, heads: int, kv_heads: int, dim: int, vdim: int, key_eps: float, stream: Optional[int] = None,
+               per_head_decay: bool = False) -> None:
     """Delta rule with a decay per head and key channel over the step's runs; the state [slots, >= heads dim vdim]
     fp32 is read and left updated (``T`` tokens in ``S`` runs; T == S, a decode step, takes small blocks).  ``conv`` fp32 [T, q | k | v] after convolution and silu, ``beta`` logits at
-    column beta_col, decay logits at column a_col of ``a``; out fp32 [T, heads vdim]."""
+    column beta_col, decay logits at column a_col of ``a``; out fp32 [T, heads vdim].  ``per_head_decay``: one decay
+    logit (and one ``dt_bias``) per head instead of per head and key channel."""
     for t, n in ((conv, "conv"), (beta, "beta"), (a, "a"), (dt_bias, "dt_bias"), (A_log, "A_log"), (state, "state"), (out, "out")):
         _check(t, n, torch.float32)
     _check_runs(query_start, slots, S)
     if conv.shape[1] != 2 * kv_heads * dim + heads * vdim or beta_col + heads > beta.shape[1] or \
-            a_col + heads * dim > a.shape[1] or dt_bias.numel() != heads * dim or A_log.numel() != heads or \
+            a_col + heads * (1 if per_head_decay else dim) > a.shape[1] or \
+            dt_bias.numel() != heads * (1 if per_head_decay else dim) or A_log.numel() != heads or \
             state.dim() != 2 or state.shape[1] < heads * dim * vdim:
         raise KernelError("delta_scan: buffers do not fit the head geometry")
     lib = _lib("recurrent")
     _call(lib, lib.ember_delta_scan, _p(conv), c_int(conv.shape[1]), _off(beta, beta_col), c_int(beta.shape[1]), _off(a, a_col),
           c_int(a.shape[1]), _p(dt_bias), _p(A_log), _p(state), c_longlong(state.shape[1]), _p(out), _p(query_start), _p(slots),
-          c_int(T), c_int(S), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(key_eps), _stream(stream))
+          c_int(T), c_int(S), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), c_float(key_eps),
+          c_int(1 if per_head_decay else 0), _stream(stream))
 
 
 def memory_scan(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, off_i: int, off_f: int, bias_i: torch.Tensor,
@@ -985,6 +1035,57 @@ def _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, what):
                           f"[pages, {kv_heads}, {page}, {dim} | {vdim}]")
 
 
+def _check_head_gate(head_gate, T: int, heads: int) -> None:
+    if head_gate is not None:
+        _check(head_gate, "head_gate", torch.float32)
+        if head_gate.dim() != 2 or head_gate.shape[0] < T or head_gate.shape[1] < heads:
+            raise KernelError(f"attention: a head gate of {tuple(head_gate.shape)} for {T} tokens of {heads} heads")
+
+
+def head_prepare_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], norm_mode: str, q_w: Optional[torch.Tensor],
+                       k_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rotary: int, q_temp_coef: float,
+                       q_temp_every: int, T: int, heads: int, kv_heads: int, dim: int, vdim: int, positions: torch.Tensor,
+                       seq_of: torch.Tensor, block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                       q_out: torch.Tensor, write_kv: bool = True, err: Optional[torch.Tensor] = None,
+                       stream: Optional[int] = None) -> None:
+    """A token's q/k/v (``qkv`` fp32 [T, q | k | v], plus ``bias``) made ready for attention: an RMS norm of queries and
+    keys (``norm_mode`` "none", "whole": over the whole projection with weights of that size, "head": per head with
+    weights of ``dim`` shared by the heads), the rotation of the first ``rotary`` elements of every query and key head
+    (element i with i + rotary / 2, angle position * inv_freq[i]), the query times
+    1 + q_temp_coef * ln(floor((position + 1) / q_temp_every) + 1) (``q_temp_every`` 0: not); queries to ``q_out``, keys and
+    values into the token's page."""
+    _check(qkv, "qkv", torch.float32)
+    modes = {"none": 0, "whole": 1, "head": 2}
+    if norm_mode not in modes:
+        raise KernelError(f"head_prepare_store: norm mode {norm_mode!r}")
+    qn, kn = heads * dim, kv_heads * dim
+    for t, n, size in ((bias, "bias", qn + kn + kv_heads * vdim), (q_w, "q_w", qn if norm_mode == "whole" else dim),
+                       (k_w, "k_w", kn if norm_mode == "whole" else dim), (inv_freq, "inv_freq", rotary // 2)):
+        if t is not None:
+            _check(t, n, torch.float32)
+            if t.numel() != size:
+                raise KernelError(f"head_prepare_store: {n} has {t.numel()} elements, not {size}")
+    if norm_mode != "none" and (q_w is None or k_w is None):
+        raise KernelError("head_prepare_store: a norm needs its weights")
+    if rotary and inv_freq is None:
+        raise KernelError("head_prepare_store: a rotation needs its frequencies")
+    _check(positions, "positions", torch.int32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    _check(q_out, "q_out")
+    _check(k_pool, "k_pool", q_out.dtype)
+    _check(v_pool, "v_pool", q_out.dtype)
+    _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, "head_prepare_store")
+    if qkv.dim() != 2 or qkv.shape[0] < T or qkv.shape[1] < qn + kn + kv_heads * vdim or q_out.numel() < T * qn:
+        raise KernelError("head_prepare_store: buffers do not fit the step")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_head_prepare_store, _p(qkv), c_int(qkv.shape[1]), _p(bias), c_int(modes[norm_mode]), _p(q_w), _p(k_w),
+          c_float(eps), _p(inv_freq), c_int(rotary), c_float(q_temp_coef), c_int(q_temp_every), c_int(T), c_int(heads), c_int(kv_heads),
+          c_int(dim), c_int(vdim), _p(positions), _p(seq_of), _p(block_table), c_int(block_table.shape[-1]), c_int(page),
+          c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool), c_int(dtype_code(q_out.dtype)), c_int(1 if write_kv else 0),
+          _p(err), _stream(stream))
+
+
 def whole_norm_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor],
                      eps: float, T: int, heads: int, kv_heads: int, dim: int, vdim: int, positions: torch.Tensor,
                      seq_of: torch.Tensor, block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
@@ -1098,10 +1199,15 @@ def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch
                    kv_heads: int, dim: int, vdim: int, tiles: torch.Tensor, n_tiles: int, tile_q: int, block_table: torch.Tensor,
                    page: int, window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
                    split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                   err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+                   err: Optional[torch.Tensor] = None, stream: Optional[int] = None, chunk: int = 0,
+                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None) -> None:
     """out[t, h] = sum_j w_j v_j over the visible keys j <= t (under a window: t - j < window or j < keep_first), w the
     softmax of scale * q . k_j whose denominator also holds exp(sink[h]).  Keys [.., dim], values [.., vdim]; without
-    ``v_pool`` a value is the first ``vdim`` elements of the key row.  ``out`` is q's dtype or float32."""
+    ``v_pool`` a value is the first ``vdim`` elements of the key row.  ``out`` is q's dtype or float32.  ``chunk`` > 0:
+    j is visible only if floor(t / chunk) == floor(j / chunk) (positions, counted from the sequence's start);
+    ``softcap`` > 0: the scaled score becomes softcap * tanh(score / softcap); ``head_gate`` (fp32 [T, >= heads] logits):
+    head h's output is multiplied by sigmoid(head_gate[t, h])."""
+    _check_head_gate(head_gate, T, heads)
     _check(q, "q")
     _check(k_pool, "k_pool", q.dtype)
     if v_pool is not None:
@@ -1128,7 +1234,8 @@ def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch
           c_int(1 if out.dtype == torch.float32 else 0), c_int(T), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles),
           c_int(n_tiles), c_int(tile_q), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]),
           c_int(window), c_int(keep_first), _p(sink), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml),
-          _p(err), _stream(stream))
+          _p(err), c_int(chunk), c_float(softcap), _p(head_gate), c_int(head_gate.shape[-1] if head_gate is not None else 0),
+          _stream(stream))
 
 
 # --------------------------------------------------------------------- routed feed-forward (csrc/moe.cu)
@@ -1152,13 +1259,21 @@ def _route_rule(rule, experts: int):
     """(sigmoid, correction pointer, scale, renormalize) of a routing rule: None is the softmax over the chosen logits;
     else (correction fp32 [experts] or None, scale, renormalize) for sigmoid scores."""
     if rule is None:
-        return c_int(0), c_void_p(0), c_float(1.0), c_int(0)
-    correction, scale, renormalize = rule
+        return c_int(0), c_void_p(0), c_float(1.0), c_int(0), c_int(0), c_int(0)
+    correction, scale, renormalize = rule[:3]
+    # longer rules: (..., scoring, groups, keep) with scoring "sigmoid" or "softmax" (over all experts) and the choice
+    # limited to the ``keep`` best of ``groups`` equal groups of neighbouring experts (groups 0: no limit)
+    scoring, groups, keep = (tuple(rule[3:]) + ("sigmoid", 0, 0)[len(rule) - 3:]) if len(rule) > 3 else ("sigmoid", 0, 0)
+    if scoring not in ("sigmoid", "softmax"):
+        raise KernelError(f"routing: scoring {scoring!r}")
+    if groups and (groups > 32 or experts % groups or not 1 <= keep <= groups):
+        raise KernelError(f"routing: {groups} groups (at most 32, dividing {experts} experts) of which {keep} are kept")
     if correction is not None:
         _check(correction, "correction", torch.float32)
         if correction.numel() != experts:
             raise KernelError(f"routing: a correction of {correction.numel()} for {experts} experts")
-    return c_int(1), _p(correction), c_float(scale), c_int(1 if renormalize else 0)
+    return (c_int(1 if scoring == "sigmoid" else 2), _p(correction), c_float(scale), c_int(1 if renormalize else 0), c_int(groups),
+            c_int(keep))
 
 
 def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor, stream: Optional[int] = None,
@@ -1178,10 +1293,12 @@ def moe_route(logits: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: to
 
 
 def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
-              slot_of_pair: torch.Tensor, tiles: torch.Tensor, tile_rows: int = MOE_TILE_ROWS, stream: Optional[int] = None) -> int:
+              slot_of_pair: torch.Tensor, tiles: torch.Tensor, tile_rows: int = MOE_TILE_ROWS, stream: Optional[int] = None,
+              tiled: int = 0) -> int:
     """Orders the (token, choice) pairs by expert.  offsets int32 [experts + 1]; pair_of_slot, slot_of_pair int32
     [n_pairs]; tiles int32 [1 + 2 max_tiles]: the number of row tiles (of up to ``tile_rows`` slots of one expert),
-    then every tile's expert, then every tile's first slot.  Returns max_tiles (what the products' grids are sized for)."""
+    then every tile's expert, then every tile's first slot.  Returns max_tiles (what the products' grids are sized for).
+    ``tiled`` > 0: only the first ``tiled`` experts have weights; the others' pairs get slots but no tiles."""
     for t, n in ((sel, "sel"), (offsets, "offsets"), (pair_of_slot, "pair_of_slot"), (slot_of_pair, "slot_of_pair"), (tiles, "tiles")):
         _check(t, n, torch.int32)
     mt = moe_max_tiles(n_pairs, experts, tile_rows)
@@ -1190,21 +1307,24 @@ def moe_group(sel: torch.Tensor, n_pairs: int, experts: int, offsets: torch.Tens
         raise KernelError("moe_group: buffers do not fit the step")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_group, _p(sel), c_int(n_pairs), c_int(experts), _p(offsets), _p(pair_of_slot), _p(slot_of_pair),
-          _off(tiles, 0), _off(tiles, 1), _off(tiles, 1 + mt), c_int(mt), c_int(tile_rows), _stream(stream))
+          _off(tiles, 0), _off(tiles, 1), _off(tiles, 1 + mt), c_int(mt), c_int(tile_rows), c_int(tiled), _stream(stream))
     return mt
 
 
 def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor, pair_of_slot: torch.Tensor,
              tiles: torch.Tensor, max_tiles: int, top: int, gated: bool, limit: float = 0.0, alpha: float = 1.0,
-             stream: Optional[int] = None, streaming: bool = False, up_offset: float = 1.0) -> None:
+             stream: Optional[int] = None, streaming: bool = False, up_offset: float = 1.0, square_relu: bool = False) -> None:
     """The product of every slot's row with its expert's matrix (``w`` [experts, N, K]).  ``top`` > 0: a slot's row of
     ``x`` is its token's (x [tokens, K], gathered through the pairs); 0: x has a row per slot.  ``gated``: w's rows are
     interleaved (gate, up) and out[slot, j] = g sigmoid(alpha g) (u + up_offset) with g = min(gate, limit),
-    u = clamp(up, -limit, limit) (``limit`` may be infinite), in x's dtype; else out[slot] is the fp32 product.  ``streaming``: the form for tile
+    u = clamp(up, -limit, limit) (``limit`` may be infinite), in x's dtype; else out[slot] is the fp32 product, or with
+    ``square_relu`` relu(product)^2 in x's dtype (an ungated expert's activation).  ``streaming``: the form for tile
     lists of 16-row tiles (``moe_group`` with ``MOE_STREAM_ROWS``), else the form for 32-row tiles."""
     _check(x, "x")
     _check(w, "w", x.dtype)
-    _check(out, "out", x.dtype if gated else torch.float32)
+    if gated and square_relu:
+        raise KernelError("moe_gemm: relu^2 is the activation of an ungated product")
+    _check(out, "out", x.dtype if (gated or square_relu) else torch.float32)
     E, N, K = w.shape
     n_out = N // 2 if gated else N
     if x.shape[-1] != K or out.shape[-1] != n_out:
@@ -1213,12 +1333,15 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch
     _call(lib, lib.ember_moe_stream if streaming else lib.ember_moe_gemm, _p(x), c_int(dtype_code(x.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)), c_longlong(N * K),
           _p(out), c_int(dtype_code(out.dtype)), c_int(n_out), _p(offsets), _p(pair_of_slot), _off(tiles, 0), _off(tiles, 1),
           _off(tiles, 1 + max_tiles), c_int(max_tiles), c_int(top), c_int(N), c_int(K), c_int(1 if gated else 0), c_float(limit),
-          c_float(alpha), c_float(up_offset), _stream(stream))
+          c_float(alpha), c_float(up_offset), c_int(1 if square_relu else 0), _stream(stream))
 
 
 def moe_combine(y: torch.Tensor, wgt: torch.Tensor, slot_of_pair: torch.Tensor, T: int, top: int, out: torch.Tensor,
-                accumulate: bool = False, stream: Optional[int] = None) -> None:
-    """out[t] (+)= sum over the token's choices, in order, of wgt[t, k] * y[slot of (t, k)]; all fp32."""
+                accumulate: bool = False, stream: Optional[int] = None, sel: Optional[torch.Tensor] = None, experts: int = 0,
+                same: Optional[torch.Tensor] = None) -> None:
+    """out[t] (+)= sum over the token's choices, in order, of wgt[t, k] * y[slot of (t, k)]; all fp32.  With ``sel``
+    (the choices) a choice from ``experts`` on is an identity expert, whose output is the token's row of ``same``
+    (fp32 or bfloat16 [T, hidden]) instead of a row of y."""
     _check(y, "y", torch.float32)
     _check(wgt, "wgt", torch.float32)
     _check(out, "out", torch.float32)
@@ -1226,9 +1349,15 @@ def moe_combine(y: torch.Tensor, wgt: torch.Tensor, slot_of_pair: torch.Tensor, 
     hidden = out.shape[-1]
     if y.shape[-1] != hidden or y.numel() < T * top * hidden or out.numel() < T * hidden:
         raise KernelError("moe_combine: buffers do not fit the step")
+    if sel is not None:
+        _check(sel, "sel", torch.int32)
+        _check(same, "same")
+        if same.dtype not in (torch.float32, torch.bfloat16) or same.shape[-1] != hidden or same.numel() < T * hidden or sel.numel() < T * top:
+            raise KernelError("moe_combine: the identity experts' rows do not fit the step")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_combine, _p(y), _p(wgt), _p(slot_of_pair), c_int(T), c_int(top), _p(out), c_int(1 if accumulate else 0),
-          c_int(hidden), _stream(stream))
+          c_int(hidden), _p(sel), c_int(experts), _p(same if sel is not None else None),
+          c_int(dtype_code(same.dtype) if sel is not None else 0), _stream(stream))
 
 
 def moe_gather(x: torch.Tensor, pair_of_slot: torch.Tensor, n_pairs: int, top: int, xs: torch.Tensor, stream: Optional[int] = None) -> None:
@@ -1244,16 +1373,31 @@ def moe_gather(x: torch.Tensor, pair_of_slot: torch.Tensor, n_pairs: int, top: i
 
 
 def moe_activation(gu: torch.Tensor, act: torch.Tensor, rows: int, limit: float, alpha: float, stream: Optional[int] = None,
-                   up_offset: float = 1.0) -> None:
-    """act[r, j] = g sigmoid(alpha g) (u + up_offset) with g = min(gu[r, 2j], limit), u = clamp(gu[r, 2j + 1], -limit, limit); gu fp32."""
+                   up_offset: float = 1.0, bias: Optional[torch.Tensor] = None) -> None:
+    """act[r, j] = g sigmoid(alpha g) (u + up_offset) with g = min(gu[r, 2j], limit), u = clamp(gu[r, 2j + 1], -limit, limit); gu fp32.
+    ``bias`` (fp32 [2n], interleaved like a row of gu) is added to gu first."""
     _check(gu, "gu", torch.float32)
     _check(act, "act")
     n = act.shape[-1]
     if gu.shape[-1] != 2 * n or gu.numel() < rows * 2 * n or act.numel() < rows * n:
         raise KernelError("moe_activation: buffers do not fit")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != 2 * n:
+            raise KernelError("moe_activation: the biases do not fit the rows")
     lib = _lib("moe")
     _call(lib, lib.ember_moe_activation, _p(gu), _p(act), c_int(dtype_code(act.dtype)), c_longlong(rows * n), c_float(limit),
-          c_float(alpha), c_float(up_offset), _stream(stream))
+          c_float(alpha), c_float(up_offset), _p(bias), c_int(n), _stream(stream))
+
+
+def moe_square_relu(x: torch.Tensor, act: torch.Tensor, n: int, stream: Optional[int] = None) -> None:
+    """act[:n] = relu(x[:n])^2 (x fp32): the activation of an ungated expert whose product left fp32 sums."""
+    _check(x, "x", torch.float32)
+    _check(act, "act")
+    if x.numel() < n or act.numel() < n:
+        raise KernelError("moe_square_relu: buffers do not fit")
+    lib = _lib("moe")
+    _call(lib, lib.ember_moe_square_relu, _p(x), _p(act), c_int(dtype_code(act.dtype)), c_longlong(n), _stream(stream))
 
 
 def moe_router(x: torch.Tensor, w: torch.Tensor, T: int, top: int, sel: torch.Tensor, wgt: torch.Tensor,
@@ -1295,8 +1439,10 @@ def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optio
                             vdim: int, tiles: torch.Tensor, n_tiles: int, tile_q: int, block_table: torch.Tensor, page: int,
                             window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
                             split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                            err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+                            err: Optional[torch.Tensor] = None, stream: Optional[int] = None, chunk: int = 0,
+                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None) -> None:
     """``sink_attention`` on the tensor cores (bfloat16 queries, keys, values; scores, weights and sums fp32)."""
+    _check_head_gate(head_gate, T, heads)
     _check(q, "q", torch.bfloat16)
     _check(k_pool, "k_pool", torch.bfloat16)
     if v_pool is not None:
@@ -1322,4 +1468,5 @@ def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optio
     _call(lib, lib.ember_shared_row_attention_tc, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(1 if out.dtype == torch.float32 else 0), c_int(T),
           c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles), c_int(n_tiles), c_int(tile_q), _p(block_table),
           c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), c_int(window), c_int(keep_first), _p(sink),
-          c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml), _p(err), _stream(stream))
+          c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml), _p(err), c_int(chunk), c_float(softcap),
+          _p(head_gate), c_int(head_gate.shape[-1] if head_gate is not None else 0), _stream(stream))

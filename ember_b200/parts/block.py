@@ -240,6 +240,70 @@ class ConnectedPreNormBlock(Arrangement):
                            p["feed_forward_connection"], store)
 
 
+class PostNormBlock(Arrangement):
+    """The norm after the sum, with a scaled stream:
+
+        h = mixer_norm(alpha * h + mixer(h));  h = feed_forward_norm(alpha * h + feed_forward(h))
+
+    The sublayers read the stream itself (float32: the stream's buffer; bfloat16: the stream rounded once, which the
+    fused scale + add + norm of the sublayer before leaves beside the new rows).  A layer may have no feed-forward.
+    ``alpha`` is the arrangement's one constant (``LayerSpec.constants``, name "alpha"; 1 if absent).  The sublayer stores its fp32 result in a buffer
+    (``can_store``; others add into a zeroed one); scale, addition, norm and the rounded copy are one kernel (the norm's
+    ``scaled_add``), which also adds the bias a feed-forward's last product left out (``result_bias``).  A feed-forward
+    that wants the fp32 stream beside its rounded input (identity experts) gets it as ``stream=``."""
+
+    ROLES = {"mixer": "mixer", "mixer_norm": "norm", "feed_forward": "feed_forward", "feed_forward_norm": "norm"}
+    OPTIONAL = frozenset({"feed_forward", "feed_forward_norm"})
+
+    def __init__(self, layer_spec):
+        super().__init__(layer_spec)
+        p = self.parts
+        self.alpha = layer_spec.constant("alpha", 1.0)
+        if ("feed_forward" in p) != ("feed_forward_norm" in p):
+            raise ConfigError("a post-norm layer has a feed-forward with its norm, or neither")
+        for role in ("mixer_norm", "feed_forward_norm"):
+            if role in p and not hasattr(p[role], "scaled_add"):
+                raise ConfigError(f"the norm in the role {role!r} cannot scale, add and norm in one kernel (no scaled_add)")
+
+    def _input(self, ctx, h):
+        """What a sublayer reads, and the bfloat16 buffer the next fused norm fills (None on the float32 path)."""
+        if self.rt.dtype == torch.float32:
+            return h, None
+        r = ctx.buf("block.stream_rounded", (ctx.max_tokens, h.shape[-1]), torch.bfloat16)
+        at = ctx.memo.get("schedule.index")
+        made = ctx.memo.get("block.stream_rounded.at")
+        if at is None or made is None or made not in (at, at - 1) or ctx.memo.get("block.stream_rounded.of") != h.data_ptr():
+            ops.round_rows(h, r, ctx.T * h.shape[-1], stream=ctx.stream)
+        return r, r
+
+    def _sublayer(self, ctx, h, part, norm, run) -> None:
+        T, hidden = ctx.T, h.shape[-1]
+        y = ctx.buf("block.sublayer", (ctx.max_tokens, hidden), torch.float32)
+        x, rounded = self._input(ctx, h)
+        if not getattr(part, "can_store", False):
+            y[:T].zero_()
+        run(x, y)
+        norm.scaled_add(ctx, y, h, T, self.alpha, y_bias=getattr(part, "result_bias", None), rounded=rounded)
+        if rounded is not None:
+            ctx.memo["block.stream_rounded.at"] = ctx.memo.get("schedule.index")
+            ctx.memo["block.stream_rounded.of"] = h.data_ptr()
+
+    def forward(self, ctx, h: torch.Tensor, caches, owns_cache: bool = True) -> None:
+        p = self.parts
+        mixer = p["mixer"]
+        kw = {"accumulate": False} if getattr(mixer, "can_store", False) else {}
+        self._sublayer(ctx, h, mixer, p["mixer_norm"], lambda x, y: mixer.forward(ctx, x, y, self.cache_of(caches), owns_cache, **kw))
+        ff = p.get("feed_forward")
+        if ff is not None:
+            kw = {"accumulate": False} if getattr(ff, "can_store", False) else {}
+            if getattr(ff, "result_bias", None) is not None:
+                kw["fold_bias"] = True
+            if getattr(getattr(ff, "spec", None), "identity", 0):
+                kw["stream"] = h
+            self._sublayer(ctx, h, ff, p["feed_forward_norm"], lambda x, y: ff.forward(ctx, x, y, **kw))
+
+
 register_part("arrangement", "prenorm", PreNormBlock)
+register_part("arrangement", "postnorm", PostNormBlock)
 register_part("arrangement", "connected_prenorm", ConnectedPreNormBlock)
 register_part("arrangement", "gated_sandwich", GatedSandwichBlock)

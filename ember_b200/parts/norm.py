@@ -41,6 +41,13 @@ class RMSNorm(Norm):
         ops.gated_norm_add(y, gate_logits, self.weight, None, self.spec.eps, False, residual, n_rows, gate_bias=gate_bias,
                            rounded=rounded, stream=ctx.stream)
 
+    def scaled_add(self, ctx, y: torch.Tensor, residual: torch.Tensor, n_rows: int, alpha: float,
+                   y_bias: Optional[torch.Tensor] = None, rounded: Optional[torch.Tensor] = None) -> None:
+        """residual = norm(alpha * residual + y + y_bias) in one kernel, in place: the norm after the residual sum;
+        ``rounded`` (bfloat16) also receives the new rows."""
+        ops.scaled_add_norm(y, y_bias, alpha, self.weight, None, self.spec.eps, False, residual, n_rows, rounded=rounded,
+                            stream=ctx.stream)
+
 
 class LayerNorm(Norm):
     """out = (x - mean) / sqrt(var + eps) * weight + bias, var = mean((x - mean)^2), statistics in fp32."""
@@ -50,18 +57,31 @@ class LayerNorm(Norm):
     def _names(self):
         return self.prefix + self.spec.weight_suffix, self.prefix + self.spec.bias_suffix
 
+    def _has_bias(self) -> bool:
+        return bool(getattr(self.spec, "bias", True))
+
     def weight_decls(self) -> List[WeightDecl]:
         w, b = self._names()
-        return [WeightDecl(w, (self.spec.size,), init="norm"), WeightDecl(b, (self.spec.size,), init="zeros")]
+        return [WeightDecl(w, (self.spec.size,), init="norm")] + ([WeightDecl(b, (self.spec.size,), init="zeros")] if self._has_bias() else [])
 
     def load(self, store, rt: Runtime) -> None:
-        w, b = (store.take(n, (self.spec.size,)) for n in self._names())
+        names = self._names()
+        w = store.take(names[0], (self.spec.size,))
+        b = store.take(names[1], (self.spec.size,)) if self._has_bias() else None
         self.weight = rt.to_device(w, torch.float32) if w is not None else None
         self.bias = rt.to_device(b, torch.float32) if b is not None else None
 
     def scale_output(self, scale: float) -> None:
         if self.weight is not None:
-            self.weight, self.bias = self.weight * scale, self.bias * scale
+            self.weight = self.weight * scale
+            self.bias = self.bias * scale if self.bias is not None else None
+
+    def scaled_add(self, ctx, y: torch.Tensor, residual: torch.Tensor, n_rows: int, alpha: float,
+                   y_bias: Optional[torch.Tensor] = None, rounded: Optional[torch.Tensor] = None) -> None:
+        """residual = norm(alpha * residual + y + y_bias) in one kernel, in place: the norm after the residual sum;
+        ``rounded`` (bfloat16) also receives the new rows."""
+        ops.scaled_add_norm(y, y_bias, alpha, self.weight, self.bias, self.spec.eps, True, residual, n_rows, rounded=rounded,
+                            stream=ctx.stream)
 
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
         ops.layer_norm(x, self.weight, self.bias, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)

@@ -53,6 +53,11 @@ class RotaryEmbedding(PositionEncoding):
 
     def inv_freq(self) -> np.ndarray:
         r = self.spec.rotary_dim
+        linear = float(getattr(self.spec, "linear_factor", 1.0))
+        if linear != 1.0:                               # every frequency divided by the factor, in float64, rounded once
+            if not linear > 0 or getattr(self.spec, "scaling_factor", 0.0):
+                raise ConfigError("linear rotary scaling needs a positive factor and excludes the stretched frequencies")
+            return (np.power(float(self.spec.theta), -2.0 * np.arange(r // 2, dtype=np.float64) / r) / linear).astype(np.float32)
         if getattr(self.spec, "scaling_factor", 0.0):
             f = np.power(float(self.spec.theta), -2.0 * np.arange(r // 2, dtype=np.float64) / r)
             return self._scaled(f).astype(np.float32)
@@ -71,7 +76,7 @@ class RotaryEmbedding(PositionEncoding):
         s = self.spec
         return (s.rotary_dim, float(s.theta), getattr(s, "frequency_precision", "float32"), getattr(s, "layout", "half"),
                 getattr(s, "scaling_factor", 0.0), getattr(s, "scaling_original", 0.0), getattr(s, "scaling_fast", 0.0),
-                getattr(s, "scaling_slow", 0.0))
+                getattr(s, "scaling_slow", 0.0), getattr(s, "linear_factor", 1.0))
 
 
 class NoPosition(PositionEncoding):

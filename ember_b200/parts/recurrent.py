@@ -58,7 +58,11 @@ class GatedDelta(_StateMixer):
 
     then o / rms(o) * norm * sigmoid(W_g2 W_g1 x) and the output product.  q, k, v each pass a short causal
     convolution and silu first.  Tensors under the prefix: q, k, v (+ ``.conv``), b, a1, a2, dt_bias, A_log, g1, g2,
-    norm, o."""
+    norm, o.
+
+    ``decay`` "head": g = exp(-exp(A_log[h]) * softplus(W_a x + dt_bias[h])), one number per head (tensor ``a`` [heads,
+    hidden] instead of a1 / a2, ``dt_bias`` [heads]).  ``gate`` "silu": o / rms(o) * norm * silu(W_g x) with a full-rank
+    ``g`` [heads vdim, hidden] instead of g1 / g2."""
 
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -67,9 +71,13 @@ class GatedDelta(_StateMixer):
             raise ConfigError(f"{s.num_heads} value heads do not divide into {s.num_kv_heads} query/key heads")
         if min(s.head_dim, s.value_dim, s.conv_taps) <= 0:
             raise ConfigError("channel_delta: head sizes and convolution taps must be positive")
+        if s.decay not in ("channel", "head") or s.gate not in ("low_rank_sigmoid", "silu"):
+            raise ConfigError(f"channel_delta: decay {s.decay!r} (channel, head), gate {s.gate!r} (low_rank_sigmoid, silu)")
         self.qk, self.vd = s.num_kv_heads * s.head_dim, s.num_heads * s.value_dim
         self.channels = 2 * self.qk + self.vd
         self.decay_rank, self.gate_rank = s.decay_rank, s.gate_rank
+        self.per_head, self.full_gate = s.decay == "head", s.gate == "silu"
+        self.decays = s.num_heads if self.per_head else s.num_heads * s.head_dim
 
     def state_floats(self) -> int:
         s = self.spec
@@ -78,36 +86,44 @@ class GatedDelta(_StateMixer):
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
         H, D, hid, ra, rg = s.num_heads, s.head_dim, s.hidden_size, self.decay_rank, self.gate_rank
-        if ra <= 0 or rg <= 0:
+        if (not self.per_head and ra <= 0) or (not self.full_gate and rg <= 0):
             raise ConfigError("channel_delta: the ranks of the decay and gate projections are read from the weights at "
                               "load; a configuration that lists tensors without a file must give them")
-        return [WeightDecl(p + "q", (self.qk, hid)), WeightDecl(p + "q.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
-                WeightDecl(p + "k", (self.qk, hid)), WeightDecl(p + "k.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
-                WeightDecl(p + "v", (self.vd, hid)), WeightDecl(p + "v.conv", (self.vd, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
-                WeightDecl(p + "b", (H, hid)), WeightDecl(p + "A_log", (H,), init="uniform", lo=-1.0, hi=1.0),
-                WeightDecl(p + "norm", (s.value_dim,), init="norm"),
-                WeightDecl(p + "a1", (ra, hid)), WeightDecl(p + "a2", (H * D, ra)),
-                WeightDecl(p + "dt_bias", (H * D,), init="uniform", lo=-3.0, hi=0.0),
-                WeightDecl(p + "g1", (rg, hid)), WeightDecl(p + "g2", (self.vd, rg)), WeightDecl(p + "o", (hid, self.vd))]
+        d = [WeightDecl(p + "q", (self.qk, hid)), WeightDecl(p + "q.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+             WeightDecl(p + "k", (self.qk, hid)), WeightDecl(p + "k.conv", (self.qk, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+             WeightDecl(p + "v", (self.vd, hid)), WeightDecl(p + "v.conv", (self.vd, s.conv_taps), init="uniform", lo=-0.5, hi=0.5),
+             WeightDecl(p + "b", (H, hid)), WeightDecl(p + "A_log", (H,), init="uniform", lo=-1.0, hi=1.0),
+             WeightDecl(p + "norm", (s.value_dim,), init="norm"),
+             WeightDecl(p + "dt_bias", (self.decays,), init="uniform", lo=-3.0, hi=0.0), WeightDecl(p + "o", (hid, self.vd))]
+        d += [WeightDecl(p + "a", (H, hid))] if self.per_head else [WeightDecl(p + "a1", (ra, hid)), WeightDecl(p + "a2", (H * D, ra))]
+        d += [WeightDecl(p + "g", (self.vd, hid))] if self.full_gate else [WeightDecl(p + "g1", (rg, hid)), WeightDecl(p + "g2", (self.vd, rg))]
+        return d
 
     def load(self, store, rt: Runtime) -> None:
         s, p = self.spec, self.prefix
         self.rt = rt
-        for attr, name in (("decay_rank", "a1"), ("gate_rank", "g1")):
-            if getattr(self, attr) <= 0:                   # a size the configuration leaves to the weights
+        for attr, name, unused in (("decay_rank", "a1", self.per_head), ("gate_rank", "g1", self.full_gate)):
+            if getattr(self, attr) <= 0 and not unused:    # a size the configuration leaves to the weights
                 shape = store.shape(p + name)
                 setattr(self, attr, int(shape[0]) if shape and len(shape) == 2 else 1)
         w = self._take_all(store)
         if w is None:
             return
         ra, rg, HD = self.decay_rank, self.gate_rank, s.num_heads * s.head_dim
-        self.in_proj = self._fused([w[p + "q"], w[p + "k"], w[p + "v"], w[p + "b"]], rt)            # [q | k | v | beta]
-        self.low = self._fused([w[p + "a1"], w[p + "g1"]], rt)                                       # [a1 | g1]
-        wd = self.low.weight.dtype
-        up = torch.zeros(HD + self.vd, ra + rg, dtype=wd, device=rt.device)                          # block diagonal
-        up[:HD, :ra] = rt.to_device(w[p + "a2"], wd)
-        up[HD:, ra:] = rt.to_device(w[p + "g2"], wd)
-        self.up = Linear(up)
+        # one product for everything that is a full-rank projection of the input: [q | k | v | beta (| decay) (| gate)]
+        self.in_proj = self._fused([w[p + "q"], w[p + "k"], w[p + "v"], w[p + "b"]] + ([w[p + "a"]] if self.per_head else [])
+                                   + ([w[p + "g"]] if self.full_gate else []), rt)
+        lows = ([] if self.per_head else [("a1", "a2", HD, ra)]) + ([] if self.full_gate else [("g1", "g2", self.vd, rg)])
+        self.low = self.up = None
+        if lows:                                           # the low-rank pairs: [a1 | g1], then a block-diagonal [a2, g2]
+            self.low = self._fused([w[p + first] for first, _, _, _ in lows], rt)
+            wd = self.low.weight.dtype
+            up = torch.zeros(sum(n for _, _, n, _ in lows), sum(r for _, _, _, r in lows), dtype=wd, device=rt.device)
+            row = col = 0
+            for _, second, n, r in lows:
+                up[row:row + n, col:col + r] = rt.to_device(w[p + second], wd)
+                row, col = row + n, col + r
+            self.up = Linear(up)
         self.o = Linear.from_host(w[p + "o"], rt)
         self.taps = torch.cat([rt.to_device(w[p + n + ".conv"], torch.float32) for n in "qkv"], dim=0).contiguous()
         self.dt_bias, self.A_log, self.norm_w = (rt.to_device(w[p + n], torch.float32) for n in ("dt_bias", "A_log", "norm"))
@@ -115,21 +131,26 @@ class GatedDelta(_StateMixer):
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
         H, D, V, C = s.num_heads, s.head_dim, s.value_dim, self.channels
-        proj = ctx.buf("delta.proj", (mt, C + H), torch.float32)
-        low = ctx.buf("delta.low", (mt, self.decay_rank + self.gate_rank), rt.dtype)
-        ag = ctx.buf("delta.decay_gate", (mt, H * D + self.vd), torch.float32)
+        proj = ctx.buf("delta.proj", (mt, self.in_proj.n), torch.float32)
         conv = ctx.buf("delta.conv", (mt, C), torch.float32)
         o = ctx.buf("delta.read", (mt, self.vd), torch.float32)
         y = ctx.buf("delta.normed", (mt, self.vd), rt.dtype)
         self.in_proj(ctx, x, proj, T, ops.EPI_STORE_F32)
-        self.low(ctx, x, low, T, ops.EPI_STORE)
-        self.up(ctx, low, ag, T, ops.EPI_STORE_F32)
+        ag = None
+        if self.up is not None:
+            low = ctx.buf("delta.low", (mt, self.low.n), rt.dtype)
+            ag = ctx.buf("delta.decay_gate", (mt, self.up.n), torch.float32)
+            self.low(ctx, x, low, T, ops.EPI_STORE)
+            self.up(ctx, low, ag, T, ops.EPI_STORE_F32)
+        # where the decay logits and the gate logits are: columns of the input product, or of the low-rank pairs' result
+        a_src, a_col = (proj, C + H) if self.per_head else (ag, 0)
+        g_src, g_col = (proj, C + H + (H if self.per_head else 0)) if self.full_gate else (ag, 0 if self.per_head else H * D)
         ops.conv_silu(proj, 0, self.taps, None, cache.state, H * D * V, ctx.seq_of, ctx.query_start, ctx.state_slots, conv,
                       T, ctx.S, stream=ctx.stream)
-        ops.delta_scan(conv, proj, C, ag, 0, self.dt_bias, self.A_log, cache.state, o, ctx.query_start, ctx.state_slots,
-                       T, ctx.S, H, s.num_kv_heads, D, V, s.key_eps, stream=ctx.stream)
-        ops.group_norm_gate(o, 0, ag, H * D, self.norm_w, False, s.norm_eps, ops.GATE_SIGMOID_AFTER, y, T, H, V,
-                            stream=ctx.stream)
+        ops.delta_scan(conv, proj, C, a_src, a_col, self.dt_bias, self.A_log, cache.state, o, ctx.query_start, ctx.state_slots,
+                       T, ctx.S, H, s.num_kv_heads, D, V, s.key_eps, stream=ctx.stream, per_head_decay=self.per_head)
+        ops.group_norm_gate(o, 0, g_src, g_col, self.norm_w, False, s.norm_eps,
+                            ops.GATE_SILU_AFTER if self.full_gate else ops.GATE_SIGMOID_AFTER, y, T, H, V, stream=ctx.stream)
         self._out(ctx, y, out, accumulate)
 
 

@@ -4,7 +4,12 @@
   query projection and over the whole key projection (all heads at once, before the split into heads), no rotation,
   keys of ``head_dim`` and values of ``value_dim``, and a window that keeps the first tokens in sight: position i sees
   j <= i with i - j < window or j < keep_first.  Its cache group is of kind "window" with ``keep_first``: pages the
-  window has passed go back while the request runs, those of the kept first tokens stay.
+  window has passed go back while the request runs, those of the kept first tokens stay.  Further options of the spec
+  (each a parameter, off by default): an RMS norm per head with one weight for all heads; a short causal convolution on
+  q, k, v straight after the projection (its last inputs are a per-request state beside the pages, sub-id "conv"); a
+  rotation of queries and keys after the norm; a query temperature that grows with the logarithm of the position; a
+  tanh cap on the scaled scores; a chunked mask (i sees j only inside i's chunk of positions); a sigmoid gate per head on
+  the attention's output, computed from the mixer's input.
 * "latent_attention": queries through a low-rank latent (c_q = RMSNorm(W_dq h), q = W_uq c_q, per head
   [head_dim unrotated | rot_dim rotated]) or, with ``q_rank`` 0, straight from the input (q = W_q h); the rotated parts
   turn in neighbouring pairs or in the rotate-half layout, with the position part's frequencies (stretched for long
@@ -47,12 +52,15 @@ class _SinkSoftmax(Mixer):
     # with the general kernel, at batch 64 4.93 against 6.14 ms; tests set it higher to run the general kernel in bfloat16.
     TC_MIN_TOKENS = int(__import__("os").environ.get("EMBER_SINK_TC_MIN_TOKENS", "1"))
 
-    def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale):
+    def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale,
+                chunk: int = 0, softcap: float = 0.0, head_gate=None):
         on_tc = ctx.T >= self.TC_MIN_TOKENS and ops.shared_row_attention_tc_usable(q, v_pool, dim, vdim)
         tile_q = (ops.shared_row_attention_tc_tile_queries if on_tc else ops.sink_attention_tile_queries)(heads // kv_heads)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
         # long key ranges of a small step are cut into fixed splits so that more SMs share them
         span = ctx.max_context if window <= 0 else min(ctx.max_context, window + keep_first + tile_q)
+        if chunk > 0:
+            span = min(span, chunk + tile_q)
         n_splits, part_o, part_ml = 1, None, None
         if ctx.T <= self.SPLIT_MAX_TOKENS and span > 2 * self.SPLIT_KEYS:
             n_splits = (ctx.max_context + self.SPLIT_KEYS - 1) // self.SPLIT_KEYS
@@ -61,11 +69,11 @@ class _SinkSoftmax(Mixer):
         if on_tc:           # scores and the weighted sum on mma.sync
             ops.shared_row_attention_tc(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table,
                                         page, window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml,
-                                        err=ctx.err, stream=ctx.stream)
+                                        err=ctx.err, stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate)
         else:
             ops.sink_attention(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
                                window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml, err=ctx.err,
-                               stream=ctx.stream)
+                               stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate)
 
 
 class SinkAttention(_SinkSoftmax):
@@ -76,11 +84,19 @@ class SinkAttention(_SinkSoftmax):
             raise ConfigError(f"{s.num_heads} heads do not divide into {s.num_kv_heads} key/value heads")
         if s.head_dim <= 0 or not 0 < s.value_dim <= 512:
             raise ConfigError(f"sink attention: heads of {s.head_dim} / {s.value_dim} (values up to 512)")
-        if s.qk_norm not in ("none", "whole"):
-            raise ConfigError(f"sink attention: qk_norm {s.qk_norm!r} (none, whole)")
+        if s.qk_norm not in ("none", "whole", "head"):
+            raise ConfigError(f"sink attention: qk_norm {s.qk_norm!r} (none, whole, head)")
         if s.window < 0 or s.keep_first < 0:
             raise ConfigError("sink attention: window and keep_first must be >= 0")
+        if s.conv_taps < 0 or s.conv_taps > 64 or s.chunk < 0 or s.q_temp_every < 0 or s.softcap < 0:
+            raise ConfigError("sink attention: convolution taps (up to 64), chunk, temperature period and score cap must be >= 0")
+        if s.chunk > 0 and s.window > 0:
+            raise ConfigError("sink attention: a chunked mask and a window exclude one another")
         self.q_dim, self.k_dim, self.v_dim = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim, s.num_kv_heads * s.value_dim
+        self.channels = self.q_dim + self.k_dim + self.v_dim
+        self.position = build_part("position", s.position)
+        # the general preparation kernel serves whatever the whole-projection one does not know
+        self.general = (s.qk_norm == "head" or s.position.kind != "none" or s.q_temp_every > 0)
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
@@ -91,6 +107,13 @@ class SinkAttention(_SinkSoftmax):
                   WeightDecl(p + "v.b", (self.v_dim,), init="zeros")]
         if s.qk_norm == "whole":
             d += [WeightDecl(p + "q.norm", (self.q_dim,), init="norm"), WeightDecl(p + "k.norm", (self.k_dim,), init="norm")]
+        if s.qk_norm == "head":
+            d += [WeightDecl(p + "q.norm", (s.head_dim,), init="norm"), WeightDecl(p + "k.norm", (s.head_dim,), init="norm")]
+        if s.conv_taps > 0:
+            d += [WeightDecl(p + n + ".conv", (size, s.conv_taps), init="uniform", lo=-0.5, hi=0.5)
+                  for n, size in (("q", self.q_dim), ("k", self.k_dim), ("v", self.v_dim))]
+        if s.head_gate:
+            d.append(WeightDecl(p + "g", (s.num_heads, s.hidden_size)))
         if s.sink:
             d.append(WeightDecl(p + "sink", (s.num_heads,), init="uniform", lo=-1.0, hi=1.0))
         return d
@@ -106,15 +129,26 @@ class SinkAttention(_SinkSoftmax):
         self.o = Linear.from_host(got[p + "o"], rt)
         f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
         self.bias = torch.cat([f32(n + ".b") for n in "qkv"]).contiguous() if s.bias else None
-        self.q_norm_w = f32("q.norm") if s.qk_norm == "whole" else None
-        self.k_norm_w = f32("k.norm") if s.qk_norm == "whole" else None
+        self.q_norm_w = f32("q.norm") if s.qk_norm != "none" else None
+        self.k_norm_w = f32("k.norm") if s.qk_norm != "none" else None
         self.sink = f32("sink") if s.sink else None
+        self.taps = torch.cat([f32(n + ".conv") for n in "qkv"], dim=0).contiguous() if s.conv_taps > 0 else None
+        self.gate = Linear.from_host(got[p + "g"], rt) if s.head_gate else None
+        self.inv_freq, self.rotary = self.position.rotary_table(rt)
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
         return CacheNeed(kind="window" if s.window > 0 else "full", num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
                          window=s.window, value_dim=s.value_dim if s.value_dim != s.head_dim else 0,
                          keep_first=s.keep_first if s.window > 0 else 0)
+
+    def cache_needs(self):
+        """The pages, and with a convolution a state slot for its last ``conv_taps`` - 1 projected rows (sub-id "conv")."""
+        s = self.spec
+        needs = {"": self.cache_need()}
+        if s.conv_taps > 1:
+            needs["conv"] = CacheNeed(kind="state", state_shape=((s.conv_taps - 1) * self.channels,), state_dtype="float32")
+        return needs
 
     def tile_requests(self):
         group = self.spec.num_heads // self.spec.num_kv_heads
@@ -125,16 +159,37 @@ class SinkAttention(_SinkSoftmax):
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
         H, G, D, V = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
-        qkv = ctx.buf("sink_attention.qkv", (mt, self.q_dim + self.k_dim + self.v_dim), torch.float32)
+        conv_state = None
+        if isinstance(cache, dict):                        # pages under "", the convolution's carried rows under "conv"
+            cache, conv_state = cache[""], cache.get("conv")
+        qkv = ctx.buf("sink_attention.qkv", (mt, self.channels), torch.float32)
         q = ctx.buf("sink_attention.q", (mt, self.q_dim), rt.dtype)
         att = ctx.buf("sink_attention.out", (mt, H * V), rt.dtype)
         table = ctx.block_table(cache.group)
         self.qkv(ctx, x, qkv, T, ops.EPI_STORE_F32)
-        ops.whole_norm_store(qkv, self.bias, self.q_norm_w, self.k_norm_w, s.qk_norm_eps, T, H, G, D, V, ctx.positions,
-                             ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
-                             stream=ctx.stream)
+        if s.conv_taps > 0:
+            # (a run that only reads another layer's cache would still move its own carried rows: such a layer has a
+            # state of its own, so nothing is shared)
+            mixed = ctx.buf("sink_attention.conv", (mt, self.channels), torch.float32)
+            carry = conv_state.state if conv_state is not None else ctx.buf("sink_attention.no_carry", (1, 1), torch.float32)
+            ops.conv_silu(qkv, 0, self.taps, None, carry, 0, ctx.seq_of, ctx.query_start, ctx.state_slots, mixed, T, ctx.S,
+                          stream=ctx.stream, silu=False)
+            qkv = mixed
+        if self.general:
+            ops.head_prepare_store(qkv, self.bias, s.qk_norm, self.q_norm_w, self.k_norm_w, s.qk_norm_eps,
+                                   self.inv_freq if self.rotary else None, self.rotary, s.q_temp_coef, s.q_temp_every, T, H, G, D, V,
+                                   ctx.positions, ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache,
+                                   err=ctx.err, stream=ctx.stream)
+        else:
+            ops.whole_norm_store(qkv, self.bias, self.q_norm_w, self.k_norm_w, s.qk_norm_eps, T, H, G, D, V, ctx.positions,
+                                 ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                                 stream=ctx.stream)
+        gate = None
+        if self.gate is not None:
+            gate = ctx.buf("sink_attention.head_gate", (mt, H), torch.float32)
+            self.gate(ctx, x, gate, T, ops.EPI_STORE_F32)
         self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
-                     s.scale)
+                     s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=gate)
         self.o(ctx, att, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 
