@@ -112,13 +112,14 @@ def chunked_attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str,
     key projections, a rotation, and a sigmoid gate per head on the result."""
     T = h.shape[0]
     H, G, D, V = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    q = short_conv(lin(h, W[p + "q"]), W[p + "q.conv"])
-    k = short_conv(lin(h, W[p + "k"]), W[p + "k.conv"])
-    v = short_conv(lin(h, W[p + "v"]), W[p + "v.conv"])
+    q, k, v = lin(h, W[p + "q"]), lin(h, W[p + "k"]), lin(h, W[p + "v"])
+    if m.get("conv"):
+        q, k, v = short_conv(q, W[p + "q.conv"]), short_conv(k, W[p + "k.conv"]), short_conv(v, W[p + "v.conv"])
     q = rms_norm(q, W[p + "q.norm"], eps).reshape(T, H, D)
     k = rms_norm(k, W[p + "k.norm"], eps).reshape(T, G, D)
-    q, k = rotate_half(q, m["rot"]), rotate_half(k, m["rot"])
-    o = softmax_attention(q, k, v.reshape(T, G, V), float(m["scale"]), visible(T, int(m["mask"]["size"])))
+    if m.get("rot"):
+        q, k = rotate_half(q, m["rot"]), rotate_half(k, m["rot"])
+    o = softmax_attention(q, k, v.reshape(T, G, V), float(m["scale"]), visible(T, int((m.get("mask") or {}).get("size", 0))))
     o = o * torch.sigmoid(lin(h, W[p + "g"]))[:, :, None]
     return lin(o.reshape(T, H * V), W[p + "o"])
 
@@ -197,8 +198,8 @@ def moe_ff(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, mlp: dict) -> to
 # ------------------------------------------------------------------------------------------------- model
 def forward(config: dict, W: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, layers_out: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] of one sequence; ``layers_out`` (a list) receives the stream after every layer."""
-    eps, alpha = float(config["norm"]["eps"]), float(config["postln_alpha"])
-    x = W["embed"].to(dtype)[torch.tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
+    eps, alpha = float(config["norm"]["eps"]), float(config.get("postln_alpha", 1.0))
+    x = W["embed"].to(dtype)[torch.tensor(tokens, dtype=torch.long)] * float((config.get("embedding") or {}).get("scale", 1.0))
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         if layer["type"] == "attention":
