@@ -21,6 +21,7 @@ Other workloads of the same engine, one JSON line each (not part of the default 
     python bench.py --workload fadosun [--breakdown]   # Fadosun beside Qwen3 at equal width, feed-forward and layers
     python bench.py --workload zufusun [--breakdown]   # Zufusun (two of eight experts a token) beside Qwen3 likewise
     python bench.py --workload fomanex [--breakdown]   # Fomanex beside Zufusun (its closest relative) and Qwen3 likewise
+    python bench.py --workload pepapel [--breakdown]   # Pepapel beside Zufusun, Fadosun (its closest relatives) and Qwen3 likewise
 """
 from __future__ import annotations
 
@@ -355,12 +356,8 @@ def workload_fadosun(args, pk) -> int:
     unless --layers says otherwise; random weights): prefill of 512 and 2,048 tokens and decode steps at batch 8 and 64
     from a context of 1,024; with --breakdown instead the device time per kernel of one 2,048-token prefill and of a
     decode step at batch 64 (kernels serialised: no programmatic dependent launch, no graphs)."""
-    from ember_b200.config import FadosunConfig
     n_layers = args.layers or 8
-    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
-    fcfg = FadosunConfig.from_json({"architecture": "Fadosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-                                    "layers": [dict(FADOSUN_LAYERS[i % 4], mlp={"kind": "dense", "ff": ff}) for i in range(n_layers)]})
-    return beside_qwen3(args, pk, "fadosun", fcfg, n_layers, {"fadosun_layers": [l["type"] for l in FADOSUN_LAYERS]})
+    return beside_qwen3(args, pk, "fadosun", fadosun_config(n_layers), n_layers, {"fadosun_layers": [l["type"] for l in FADOSUN_LAYERS]})
 
 
 def zufusun_config(n_layers):
@@ -423,6 +420,47 @@ def workload_fomanex(args, pk) -> int:
                         {"fomanex_layers": [l["type"] for l in FOMANEX_LAYERS], "listed_layers": len(cfg["layers"]), "loop": cfg.get("loop"),
                          "streams": 2, "experts": 8, "top": 2, "expert_ff": QWEN3_1P7B["intermediate_size"] // 2},
                         others=[("zufusun", zufusun_config(runs))])
+
+
+def fadosun_config(n_layers):
+    from ember_b200.config import FadosunConfig
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    return FadosunConfig.from_json({"architecture": "Fadosun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                                    "layers": [dict(FADOSUN_LAYERS[i % 4], mlp={"kind": "dense", "ff": ff}) for i in range(n_layers)]})
+
+
+PEPAPEL_LAYERS = [
+    {"type": "parallel", "mixer": {
+        "left": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "conv": 4, "mask": {"size": 512},
+                 "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0}}},
+        "right": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}}},
+    {"type": "attention", "mixer": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "softcap": 50.0,
+                                    "q_temp": {"coef": 0.5, "every": 1024}}},
+]
+
+
+def pepapel_config(n_layers):
+    """``n_layers`` layers: three parallel layers (attention inside chunks of 512 beside a delta rule of 16 heads of
+    128 x 128) and one attention layer over all keys, in turn; the first layer's feed-forward is dense and of Qwen3's size,
+    the others' eight experts of half that size plus two identity experts, two a token, from three of five groups."""
+    from ember_b200.config import PepapelConfig
+    width, ff, vocab = QWEN3_1P7B["hidden_size"], QWEN3_1P7B["intermediate_size"], QWEN3_1P7B["vocab_size"]
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 8, "top": 2, "identity": 2, "groups": {"count": 5, "keep": 3}}}
+    layers = [dict(json.loads(json.dumps(PEPAPEL_LAYERS[0 if i % 4 < 3 else 1])), mlp=moe if i else {"kind": "dense", "ff": ff, "limit": 7.0})
+              for i in range(n_layers)]
+    return PepapelConfig.from_json({"architecture": "Pepapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+                                    "embedding": {"scale": 45.25}, "postln_alpha": 2.5, "layers": layers})
+
+
+def workload_pepapel(args, pk) -> int:
+    """Pepapel beside Zufusun (whose attention and experts are the like kernels), Fadosun (whose delta rule and parallel
+    layer are) and Qwen3, all at the 1.7B width and vocabulary and with as many layers (8 unless --layers says otherwise;
+    random weights): the measurements of ``--workload fadosun``."""
+    n_layers = args.layers or 8
+    return beside_qwen3(args, pk, "pepapel", pepapel_config(n_layers), n_layers,
+                        {"pepapel_layers": ["parallel", "parallel", "parallel", "attention"], "experts": 8, "identity": 2, "top": 2,
+                         "expert_ff": QWEN3_1P7B["intermediate_size"] // 2},
+                        others=[("zufusun", zufusun_config(n_layers)), ("fadosun", fadosun_config(n_layers))])
 
 
 def beside_qwen3(args, pk, label, fcfg, n_layers, extra, others=()) -> int:
@@ -667,9 +705,9 @@ def main() -> int:
                     help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
-    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun", "zufusun", "fomanex"],
+    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b", "fadosun", "zufusun", "fomanex", "pepapel"],
                     help="default: the Qwen3-1.7B line; serving-8b and qwen3-32b are BASELINE's fourth "
-                         "and fifth configurations; fadosun, zufusun, fomanex: that design beside Qwen3 at equal sizes (with "
+                         "and fifth configurations; fadosun, zufusun, fomanex, pepapel: that design beside Qwen3 at equal sizes (with "
                          "--breakdown also per kernel); one JSON line each")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
@@ -717,6 +755,8 @@ def main() -> int:
         return workload_zufusun(args, pk)
     if args.workload == "fomanex":
         return workload_fomanex(args, pk)
+    if args.workload == "pepapel":
+        return workload_pepapel(args, pk)
     if args.breakdown:
         return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:

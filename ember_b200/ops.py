@@ -1035,11 +1035,11 @@ def _check_pages(k_pool, v_pool, kv_heads, page, dim, vdim, what):
                           f"[pages, {kv_heads}, {page}, {dim} | {vdim}]")
 
 
-def _check_head_gate(head_gate, T: int, heads: int) -> None:
+def _check_head_gate(head_gate, T: int, heads: int, col: int = 0) -> None:
     if head_gate is not None:
         _check(head_gate, "head_gate", torch.float32)
-        if head_gate.dim() != 2 or head_gate.shape[0] < T or head_gate.shape[1] < heads:
-            raise KernelError(f"attention: a head gate of {tuple(head_gate.shape)} for {T} tokens of {heads} heads")
+        if head_gate.dim() != 2 or head_gate.shape[0] < T or col < 0 or head_gate.shape[1] < col + heads:
+            raise KernelError(f"attention: a head gate of {tuple(head_gate.shape)} from column {col} for {T} tokens of {heads} heads")
 
 
 def head_prepare_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], norm_mode: str, q_w: Optional[torch.Tensor],
@@ -1200,14 +1200,14 @@ def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch
                    page: int, window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
                    split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                    err: Optional[torch.Tensor] = None, stream: Optional[int] = None, chunk: int = 0,
-                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None) -> None:
+                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, head_gate_col: int = 0) -> None:
     """out[t, h] = sum_j w_j v_j over the visible keys j <= t (under a window: t - j < window or j < keep_first), w the
     softmax of scale * q . k_j whose denominator also holds exp(sink[h]).  Keys [.., dim], values [.., vdim]; without
     ``v_pool`` a value is the first ``vdim`` elements of the key row.  ``out`` is q's dtype or float32.  ``chunk`` > 0:
     j is visible only if floor(t / chunk) == floor(j / chunk) (positions, counted from the sequence's start);
     ``softcap`` > 0: the scaled score becomes softcap * tanh(score / softcap); ``head_gate`` (fp32 [T, >= heads] logits):
-    head h's output is multiplied by sigmoid(head_gate[t, h])."""
-    _check_head_gate(head_gate, T, heads)
+    head h's output is multiplied by sigmoid(head_gate[t, head_gate_col + h])."""
+    _check_head_gate(head_gate, T, heads, head_gate_col)
     _check(q, "q")
     _check(k_pool, "k_pool", q.dtype)
     if v_pool is not None:
@@ -1234,7 +1234,7 @@ def sink_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optional[torch
           c_int(1 if out.dtype == torch.float32 else 0), c_int(T), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles),
           c_int(n_tiles), c_int(tile_q), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]),
           c_int(window), c_int(keep_first), _p(sink), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml),
-          _p(err), c_int(chunk), c_float(softcap), _p(head_gate), c_int(head_gate.shape[-1] if head_gate is not None else 0),
+          _p(err), c_int(chunk), c_float(softcap), (_off(head_gate, head_gate_col) if head_gate is not None else _p(None)), c_int(head_gate.shape[-1] if head_gate is not None else 0),
           _stream(stream))
 
 
@@ -1440,9 +1440,9 @@ def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optio
                             window: int, keep_first: int, sink: Optional[torch.Tensor], scale: float, n_splits: int = 1,
                             split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                             err: Optional[torch.Tensor] = None, stream: Optional[int] = None, chunk: int = 0,
-                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None) -> None:
+                   softcap: float = 0.0, head_gate: Optional[torch.Tensor] = None, head_gate_col: int = 0) -> None:
     """``sink_attention`` on the tensor cores (bfloat16 queries, keys, values; scores, weights and sums fp32)."""
-    _check_head_gate(head_gate, T, heads)
+    _check_head_gate(head_gate, T, heads, head_gate_col)
     _check(q, "q", torch.bfloat16)
     _check(k_pool, "k_pool", torch.bfloat16)
     if v_pool is not None:
@@ -1469,4 +1469,4 @@ def shared_row_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: Optio
           c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim), _p(tiles), c_int(n_tiles), c_int(tile_q), _p(block_table),
           c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), c_int(window), c_int(keep_first), _p(sink),
           c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml), _p(err), c_int(chunk), c_float(softcap),
-          _p(head_gate), c_int(head_gate.shape[-1] if head_gate is not None else 0), _stream(stream))
+          (_off(head_gate, head_gate_col) if head_gate is not None else _p(None)), c_int(head_gate.shape[-1] if head_gate is not None else 0), _stream(stream))

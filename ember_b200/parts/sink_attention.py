@@ -53,7 +53,7 @@ class _SinkSoftmax(Mixer):
     TC_MIN_TOKENS = int(__import__("os").environ.get("EMBER_SINK_TC_MIN_TOKENS", "1"))
 
     def _attend(self, ctx, q, k_pool, v_pool, out, table, page, heads, kv_heads, dim, vdim, window, keep_first, sink, scale,
-                chunk: int = 0, softcap: float = 0.0, head_gate=None):
+                chunk: int = 0, softcap: float = 0.0, head_gate=None, head_gate_col: int = 0):
         on_tc = ctx.T >= self.TC_MIN_TOKENS and ops.shared_row_attention_tc_usable(q, v_pool, dim, vdim)
         tile_q = (ops.shared_row_attention_tc_tile_queries if on_tc else ops.sink_attention_tile_queries)(heads // kv_heads)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
@@ -69,11 +69,13 @@ class _SinkSoftmax(Mixer):
         if on_tc:           # scores and the weighted sum on mma.sync
             ops.shared_row_attention_tc(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table,
                                         page, window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml,
-                                        err=ctx.err, stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate)
+                                        err=ctx.err, stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate,
+                                        head_gate_col=head_gate_col)
         else:
             ops.sink_attention(q, k_pool, v_pool, out, ctx.T, heads, kv_heads, dim, vdim, tiles, n_tiles, tile_q, table, page,
                                window, keep_first, sink, scale, n_splits, self.SPLIT_KEYS, part_o, part_ml, err=ctx.err,
-                               stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate)
+                               stream=ctx.stream, chunk=chunk, softcap=softcap, head_gate=head_gate,
+                                        head_gate_col=head_gate_col)
 
 
 class SinkAttention(_SinkSoftmax):
@@ -125,7 +127,8 @@ class SinkAttention(_SinkSoftmax):
         if any(v is None for v in got.values()):
             return
         wd = rt.weight_dtype(got[p + "q"].dtype)
-        self.qkv = Linear(torch.cat([rt.to_device(got[p + n], wd) for n in "qkv"], dim=0).contiguous())
+        # one product for q, k, v and, behind them, the per-head gate's logits (same input)
+        self.qkv = Linear(torch.cat([rt.to_device(got[p + n], wd) for n in ("q", "k", "v") + (("g",) if s.head_gate else ())], dim=0).contiguous())
         self.o = Linear.from_host(got[p + "o"], rt)
         f32 = lambda name: rt.to_device(got[p + name], torch.float32)          # noqa: E731
         self.bias = torch.cat([f32(n + ".b") for n in "qkv"]).contiguous() if s.bias else None
@@ -133,7 +136,6 @@ class SinkAttention(_SinkSoftmax):
         self.k_norm_w = f32("k.norm") if s.qk_norm != "none" else None
         self.sink = f32("sink") if s.sink else None
         self.taps = torch.cat([f32(n + ".conv") for n in "qkv"], dim=0).contiguous() if s.conv_taps > 0 else None
-        self.gate = Linear.from_host(got[p + "g"], rt) if s.head_gate else None
         self.inv_freq, self.rotary = self.position.rotary_table(rt)
 
     def cache_need(self) -> CacheNeed:
@@ -162,7 +164,7 @@ class SinkAttention(_SinkSoftmax):
         conv_state = None
         if isinstance(cache, dict):                        # pages under "", the convolution's carried rows under "conv"
             cache, conv_state = cache[""], cache.get("conv")
-        qkv = ctx.buf("sink_attention.qkv", (mt, self.channels), torch.float32)
+        proj = qkv = ctx.buf("sink_attention.qkv", (mt, self.qkv.n), torch.float32)      # [q | k | v (| gate logits)]
         q = ctx.buf("sink_attention.q", (mt, self.q_dim), rt.dtype)
         att = ctx.buf("sink_attention.out", (mt, H * V), rt.dtype)
         table = ctx.block_table(cache.group)
@@ -184,12 +186,8 @@ class SinkAttention(_SinkSoftmax):
             ops.whole_norm_store(qkv, self.bias, self.q_norm_w, self.k_norm_w, s.qk_norm_eps, T, H, G, D, V, ctx.positions,
                                  ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
                                  stream=ctx.stream)
-        gate = None
-        if self.gate is not None:
-            gate = ctx.buf("sink_attention.head_gate", (mt, H), torch.float32)
-            self.gate(ctx, x, gate, T, ops.EPI_STORE_F32)
         self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
-                     s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=gate)
+                     s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=proj if s.head_gate else None, head_gate_col=self.channels)
         self.o(ctx, att, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 

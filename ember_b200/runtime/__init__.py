@@ -30,7 +30,7 @@ TILE_KINDS = {"all": 0, "multi": 1, "single": 2}
 class StepLayout(ctypes.Structure):
     _fields_ = [("tokens", c_int32), ("positions", c_int32), ("seq_of", c_int32), ("query_start", c_int32),
                 ("context_len", c_int32), ("state_slots", c_int32), ("logit_rows", c_int32),
-                ("tables", c_int32 * 32), ("tiles", c_int32 * 32), ("n_tiles", c_int32 * 32), ("total", c_int32),
+                ("tables", c_int32 * 64), ("tiles", c_int32 * 64), ("n_tiles", c_int32 * 64), ("total", c_int32),
                 ("T", c_int32), ("S", c_int32), ("R", c_int32), ("max_context", c_int32)]
 
 

@@ -13,9 +13,9 @@ extern "C" {
 
 struct EmberStepLayout {     // element offsets into the packed buffer (each a multiple of 8)
     int32_t tokens, positions, seq_of, query_start, context_len, state_slots, logit_rows;
-    int32_t tables[32];      // per cache group
-    int32_t tiles[32];       // per requested tile list
-    int32_t n_tiles[32];     // rows of every tile list
+    int32_t tables[64];      // per cache group
+    int32_t tiles[64];       // per requested tile list
+    int32_t n_tiles[64];     // rows of every tile list
     int32_t total;           // ints used
     int32_t T, S, R;
     int32_t max_context;
@@ -35,7 +35,7 @@ int ember_step_layout(int n_runs, const int32_t* counts, const int32_t* starts, 
                       int n_lists, const int32_t* tile_q, const int32_t* tile_kind, int vocab, int n_prev,
                       EmberStepLayout* out) {
     if (n_runs <= 0) return -1;
-    if (n_groups > 32 || n_lists > 32) return -5;
+    if (n_groups > 64 || n_lists > 64) return -5;
     int32_t T = 0, R = 0, max_ctx = 0;
     for (int s = 0; s < n_runs; s++) {
         if (counts[s] <= 0) return -2;

@@ -168,7 +168,7 @@ def _run_mixer(spec, weights, x_all, dtype, portions=((40, 7), (3, 1), (1, 1), (
     from tests.test_parts_gpu import Bench, store_of
     part = build_part("mixer", spec, prefix)
     keys = list(part.cache_needs())
-    ident = lambda k: ("x", k) if k else 0                                    # noqa: E731
+    ident = lambda k: (0, k) if k else 0                                      # noqa: E731
     b = Bench({ident(k): v for k, v in part.cache_needs().items()}, dtype, capacity=512)
     part.load(store_of(weights), b.rt)
     hidden = x_all.shape[1]
@@ -274,7 +274,7 @@ def test_chunked_attention_alone(dtype, heads, kv, dim, vdim, hidden, taps, chun
     assert _rel(_run_mixer(spec, w, x, dtype), want) < MIX_TOL[dtype]
 
 
-@pytest.mark.parametrize("portions", [((150, 3),), ((40, 3), (1, 1), (1, 1), (1, 1), (37, 30), (2, 1), (68, 1)), ((1, 1),) * 150,
+@pytest.mark.parametrize("portions", [((150, 3),), ((40, 3), (1, 1), (1, 1), (1, 1), (37, 30), (2, 1), (68, 1)), ((38, 1),) + ((1, 1),) * 5 + ((35, 1),) + ((1, 1),) * 5 + ((35, 1),) + ((1, 1),) * 5 + ((27, 1),),
                                       ((39, 1), (1, 1), (40, 1), (40, 1), (30, 1))])
 def test_keys_just_inside_and_just_outside_a_chunk(portions):
     """Chunks of 40 with pages of 16.  The query at 40 sees itself alone and the one at 79 sees 40 .. 79: with a chunk's
