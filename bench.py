@@ -432,10 +432,10 @@ def fadosun_config(n_layers):
 PEPAPEL_LAYERS = [
     {"type": "parallel", "mixer": {
         "left": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "conv": 4, "mask": {"size": 512},
-                 "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0}}},
+                 "rot": {"dims": 64, "base": 1e6, "scaling": {"factor": 4.0}}},
         "right": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4}}},
-    {"type": "attention", "mixer": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "softcap": 50.0,
-                                    "q_temp": {"coef": 0.5, "every": 1024}}},
+    {"type": "attention", "mixer": {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 0.0884, "softcap": 30.0,
+                                    "q_temp": {"coef": 0.3, "every": 1024}}},
 ]
 
 
@@ -449,7 +449,7 @@ def pepapel_config(n_layers):
     layers = [dict(json.loads(json.dumps(PEPAPEL_LAYERS[0 if i % 4 < 3 else 1])), mlp=moe if i else {"kind": "dense", "ff": ff, "limit": 7.0})
               for i in range(n_layers)]
     return PepapelConfig.from_json({"architecture": "Pepapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-                                    "embedding": {"scale": 45.25}, "postln_alpha": 2.5, "layers": layers})
+                                    "embedding": {"scale": 45.25}, "postln_alpha": 2.0, "layers": layers})
 
 
 def workload_pepapel(args, pk) -> int:

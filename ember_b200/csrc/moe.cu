@@ -60,7 +60,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int E, int to
 // The router's product and the choice in one: logits[e] = sum_k x[t, k] w[e, k] with fp32 weights and sums.  A block
 // a token: its warps share the experts (four elements a lane and load), the first warp then chooses.
 template <typename T>
-__global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int K, int E, int top,
+__global__ void __launch_bounds__(512) moe_router_kernel(const T* __restrict__ x, const float* __restrict__ w, int K, int E, int top,
                                                          int* __restrict__ sel, float* __restrict__ wgt, float* __restrict__ logits,
                                                          RouteRule rule) {
     __shared__ float zs[MOE_MAX_EXPERTS];
@@ -100,21 +100,27 @@ __global__ void __launch_bounds__(256) moe_router_kernel(const T* __restrict__ x
 
 __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32], int E, int top, int* __restrict__ sel,
                                                float* __restrict__ wgt, int t, int lane, const RouteRule& rule) {
+    const int ns = (E + 31) >> 5;                           // slots of a lane that hold an expert: the loops below stop there
     float score[MOE_MAX_EXPERTS / 32];                      // sigmoid rule: s of the lane's experts; z becomes what is compared
     if (rule.sigmoid) {
         float zmax = -INFINITY, zsum = 0.0f;
         if (rule.sigmoid == 2) {                            // softmax over all experts
 #pragma unroll
-            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                if (i >= ns) break;
                 if (lane + 32 * i < E) zmax = fmaxf(zmax, z[i]);
+            }
             zmax = warp_max(zmax);
 #pragma unroll
-            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                if (i >= ns) break;
                 if (lane + 32 * i < E) zsum += expf(z[i] - zmax);
+            }
             zsum = warp_sum(zsum);
         }
 #pragma unroll
         for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+            if (i >= ns) break;
             const int e = lane + 32 * i;
             if (rule.sigmoid == 2) score[i] = e < E ? expf(z[i] - zmax) / zsum : 0.0f;
             else score[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.0f;
@@ -122,13 +128,19 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
         }
         if (rule.groups > 0) {                              // lane g keeps group g's best; then the best groups, one by one
             const int per = E / rule.groups;
+            int grp[MOE_MAX_EXPERTS / 32];                  // the group of each of the lane's experts (one division each)
+#pragma unroll
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                if (i >= ns) break;
+                grp[i] = lane + 32 * i < E ? (lane + 32 * i) / per : -1;
+            }
             float gbest = -INFINITY;
             for (int g = 0; g < rule.groups; g++) {
                 float b = -INFINITY;
 #pragma unroll
                 for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
-                    const int e = lane + 32 * i;
-                    if (e < E && e / per == g) b = fmaxf(b, z[i]);
+                    if (i >= ns) break;
+                    if (grp[i] == g) b = fmaxf(b, z[i]);
                 }
                 b = warp_max(b);
                 if (lane == g) gbest = b;
@@ -147,8 +159,8 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
             }
 #pragma unroll
             for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
-                const int e = lane + 32 * i;
-                if (e < E && !((kept >> (e / per)) & 1u)) z[i] = -INFINITY;
+                if (i >= ns) break;
+                if (grp[i] >= 0 && !((kept >> grp[i]) & 1u)) z[i] = -INFINITY;
             }
         }
     }
@@ -158,6 +170,7 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
         int at = 0x7fffffff;
 #pragma unroll
         for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+            if (i >= ns) break;
             const int e = lane + 32 * i;
             if (e < E && z[i] != -INFINITY && (z[i] > best || (z[i] == best && e < at))) { best = z[i]; at = e; }
         }
@@ -173,8 +186,10 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
         if (rule.sigmoid) {                                 // the chosen expert's own score, from the lane that holds it
             float sc = 0.0f;
 #pragma unroll
-            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                if (i >= ns) break;
                 if (i == (at >> 5)) sc = score[i];
+            }
             w = __shfl_sync(0xffffffffu, sc, at & 31);
         } else {
             w = expf(best - first);
@@ -184,8 +199,10 @@ __device__ __forceinline__ void choose_experts(float (&z)[MOE_MAX_EXPERTS / 32],
         if (lane == 0) sel[(size_t)t * top + k] = at;
         if (lane == (at & 31)) {
 #pragma unroll
-            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++)
+            for (int i = 0; i < MOE_MAX_EXPERTS / 32; i++) {
+                if (i >= ns) break;
                 if (i == (at >> 5)) z[i] = -INFINITY;
+            }
         }
     }
     if (lane < top) {
@@ -598,7 +615,7 @@ EMBER_API int ember_moe_router(const void* x, int x_dtype, const float* w, int T
     if (E <= 0 || E > MOE_MAX_EXPERTS || top <= 0 || top > E || top > 32 || K <= 0)
         return fail("moe_router: top %d of %d experts (at most 32 of %d), rows of %d", top, E, MOE_MAX_EXPERTS, K);
     cudaStream_t st = (cudaStream_t)stream;
-    const unsigned threads = E >= 8 ? 256 : 32 * E;           // a warp an expert, up to eight
+    const unsigned threads = 32 * (E < 16 ? E : 16);          // a warp an expert, up to sixteen (eight experts: one round, as before)
     if (x_dtype == EMBER_F32) launch_kernel(moe_router_kernel<float>, T, threads, 0, st, (const float*)x, w, K, E, top, sel, wgt, logits, rule);
     else if (x_dtype == EMBER_BF16)
         launch_kernel(moe_router_kernel<__nv_bfloat16>, T, threads, 0, st, (const __nv_bfloat16*)x, w, K, E, top, sel, wgt, logits, rule);

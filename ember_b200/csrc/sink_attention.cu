@@ -149,22 +149,26 @@ __global__ void __launch_bounds__(256) head_prepare_store_kernel(HeadPrepareArgs
         else if (p.norm_mode == 2) v *= factor[i / D] * (isq ? p.q_w[j % D] : p.k_w[j % D]);
         return v;
     };
-    auto turned = [&](int i) {
+    // element i of [q | k] after the rotation, handed to write(index, value); a rotated pair (i, i + half) is made by the
+    // thread that holds its first element, from one sine and one cosine
+    auto emit = [&](int i, float mul, auto&& write) {
         const int d = i % D;
-        float v = normed(i);
-        if (d < p.rotary) {
-            const bool low = d < half;
-            const float other = normed(low ? i + half : i - half);
+        if (d >= half && d < p.rotary) return;
+        const float v = normed(i);
+        if (d < half) {
+            const float other = normed(i + half);
             float sn, cs;
-            sincosf((float)pos * p.inv_freq[low ? d : d - half], &sn, &cs);
-            v = low ? v * cs - other * sn : v * cs + other * sn;
+            sincosf((float)pos * p.inv_freq[d], &sn, &cs);
+            write(i, (v * cs - other * sn) * mul);
+            write(i + half, (other * cs + v * sn) * mul);
+        } else {
+            write(i, v * mul);
         }
-        return v;
     };
     float temp = 1.0f;
     if (p.qt_every > 0) temp = 1.0f + p.qt_coef * logf((float)((pos + 1) / p.qt_every) + 1.0f);
     T* qo = (T*)p.q_out + (size_t)t * QN;
-    for (int i = threadIdx.x; i < QN; i += blockDim.x) qo[i] = from_float<T>(turned(i) * temp);
+    for (int i = threadIdx.x; i < QN; i += blockDim.x) emit(i, temp, [&](int j, float v) { qo[j] = from_float<T>(v); });
     if (!kv) return;
     const int seq = p.seq_of[t];
     const int blk = p.block_table[(size_t)seq * p.max_blocks + pos / p.page];
@@ -175,10 +179,11 @@ __global__ void __launch_bounds__(256) head_prepare_store_kernel(HeadPrepareArgs
     const int in_page = pos % p.page;
     T* kp = (T*)p.k_pool;
     T* vp = (T*)p.v_pool;
-    for (int i = threadIdx.x; i < KN; i += blockDim.x) {
-        const int g = i / D, d = i - g * D;
-        kp[(((size_t)blk * p.G + g) * p.page + in_page) * D + d] = from_float<T>(turned(QN + i));
-    }
+    for (int i = threadIdx.x; i < KN; i += blockDim.x)
+        emit(QN + i, 1.0f, [&](int j, float v) {
+            const int g = (j - QN) / D, d = (j - QN) - g * D;
+            kp[(((size_t)blk * p.G + g) * p.page + in_page) * D + d] = from_float<T>(v);
+        });
     for (int i = threadIdx.x; i < VN; i += blockDim.x) {
         const int g = i / p.DV, d = i - g * p.DV;
         vp[(((size_t)blk * p.G + g) * p.page + in_page) * p.DV + d] = from_float<T>(val(QN + KN + i));

@@ -147,7 +147,7 @@ def drawn_pepapel(seed: int) -> dict:
             kv = pick(1, 2, 3)
             dim = pick(16, 32, 64, 128, 24)
             mixer = _attention(kv * pick(1, 2, 4), kv, dim, pick(16, 32, 48, 64, dim), float(dim ** -0.5 * pick(1.0, 0.7)),
-                               softcap=pick(None, 5.0, 30.0, 50.0), q_temp=pick(None, (0.5, 16), (0.2, 50), (1.0, 7)))
+                               softcap=pick(None, 5.0, 30.0, 40.0), q_temp=pick(None, (0.6, 16), (0.2, 50), (1.0, 7)))
             layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
         else:
             kv, dim = pick(1, 2), pick(16, 32, 48, 64, 20)
@@ -159,4 +159,4 @@ def drawn_pepapel(seed: int) -> dict:
             right = _right(rkv * pick(1, 2), rkv, pick(16, 32, 64, 24), pick(16, 32, 64, 40), pick(2, 3, 4))
             layers.append(_parallel(left, right, mlp))
     return {"architecture": "Pepapel", "vocab": pick(384, 512, 640, 333), "width": width, "norm": {"eps": pick(1e-5, 1e-6)},
-            "embedding": {"scale": pick(1.0, 3.0, float(width ** 0.5))}, "postln_alpha": pick(1.0, 2.5, 0.8, 4.0), "layers": layers}
+            "embedding": {"scale": pick(1.0, 2.0, float(width ** 0.5))}, "postln_alpha": pick(1.0, 2.0, 0.8, 4.0), "layers": layers}

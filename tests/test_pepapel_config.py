@@ -166,3 +166,19 @@ def test_plain_delta_rule_writes_then_reads():
     v = plain.silu(torch.tensor([1.0, 2.0, 3.0], dtype=torch.float64))
     want = plain.rms_norm(v * D ** -0.5, None, 1e-6) * 30.0                  # o = v (k . q) = v / sqrt(D); rms norm; silu(30) = 30
     assert torch.allclose(y[0, :V], want, rtol=1e-5)
+
+
+def test_the_command_line_writes_and_describes_a_random_model(tmp_path, capsys):
+    """``random`` makes a folder from a config.json of this design, ``info`` reads it back through the registry."""
+    from ember_b200.cli import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(PEPAPEL["b"]["json"]))
+    out = tmp_path / "model"
+    assert main(["random", "--config", str(cfg), "--out", str(out), "--seed", "3"]) == 0
+    capsys.readouterr()
+    assert main(["info", "-m", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "pepapel: 4 layers (attention, parallel, parallel, attention)" in text and "state per request" in text
+    W = plain_inputs(str(out))[1]
+    assert W["l1.mix.right.dt_bias"].shape == (3,) and W["l1.mix.left.q.conv"].shape == (60, 1) and "l1.mix.left.g" in W
+    assert W["l1.mlp.router"].shape == (3, 100) and "l1.mlp.e1.up" in W and "l1.mlp.e2.up" not in W and "l1.mlp.e0.gate" not in W

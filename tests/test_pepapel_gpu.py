@@ -211,7 +211,7 @@ def _plain_mixer(fn, x, w, m, eps=1e-6):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv,dim,vdim,hidden,softcap,q_temp", [
     (6, 2, 16, 24, 64, 4.0, (0.5, 8)), (4, 1, 20, 12, 100, 0.0, (2.0, 1)), (2, 2, 128, 128, 128, 30.0, None),
-    (3, 3, 18, 300, 72, 1.0, (0.3, 33)), (40, 1, 8, 8, 64, 0.0, None), (8, 1, 64, 48, 64, 50.0, (0.5, 64))])
+    (3, 3, 18, 300, 72, 1.0, (0.3, 33)), (40, 1, 8, 8, 64, 0.0, None), (4, 1, 64, 32, 64, 40.0, (0.7, 64))])
 def test_attention_alone(dtype, heads, kv, dim, vdim, hidden, softcap, q_temp, attention_kernel):
     """A norm per head with one weight for all heads, no rotation, a temperature with periods of 1 to 64 positions, caps
     from one that flattens most scores to none, values wider and narrower than keys, forty query heads on one key head."""
@@ -257,7 +257,7 @@ LEFT_CASES = [
     (2, 2, 128, 128, 128, 3, 64, {"dims": 64, "base": 1e6, "scaling": {"factor": 2.0}}),
     (6, 3, 32, 48, 72, 5, 7, {"dims": 2, "base": 10.0, "scaling": {"factor": 1.0}}),     # one pair turns, chunks of seven
     (1, 1, 48, 16, 64, 2, 1, {"dims": 48, "base": 500.0}),                               # chunks of one: every token sees itself alone
-    (4, 2, 48, 48, 64, 4, 96, {"dims": 48, "base": 1e4, "scaling": {"factor": 8.0}}),    # a chunk longer than the sequence
+    (6, 2, 40, 56, 64, 3, 120, {"dims": 40, "base": 2e4, "scaling": {"factor": 3.0}}),   # a chunk longer than the sequence
 ]
 
 
