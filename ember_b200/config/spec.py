@@ -112,6 +112,7 @@ class AttentionSpec(PartSpec):
     window: int = 0               # 0 = all keys; w > 0 = the last w keys (self included)
     softmax_scale: Optional[float] = None   # None = 1/sqrt(head_dim)
     position: PartSpec = field(default_factory=NoPositionSpec)
+    softcap: float = 0.0          # > 0: score <- softcap * tanh(score / softcap) after the scale (tensor-core kernels only)
 
     @property
     def q_dim(self) -> int:

@@ -56,6 +56,7 @@ struct FaParams {
     int n_heads, n_kv;
     int window;
     float scale_log2;
+    float cap_over_scale, scale_over_cap;   // a cap on the scaled scores, cap * tanh(scale s / cap), applied to the raw scores as (cap / scale) tanh(s scale / cap); 0: no cap
     int n_tiles;
     int* err;
 };
@@ -384,6 +385,10 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             fa_tmem_ld32_nowait(tmem_s0 + lane_base + (uint32_t)((j & 1) * FA_KT + 32), su + 32);
             fa_tmem_wait_ld();
             float* s = reinterpret_cast<float*>(su);
+            if (p.cap_over_scale > 0.0f) {
+#pragma unroll
+                for (int i = 0; i < FA_KT; i++) s[i] = p.cap_over_scale * tanhf(s[i] * p.scale_over_cap);
+            }
 
             const bool interior = k0 >= lo && k0 + FA_KT <= hi && k0 + FA_KT - 1 <= pos0 &&
                                   (p.window <= 0 || k0 > pos0 + (rows - 1) / G - p.window);
@@ -550,7 +555,7 @@ EMBER_API int ember_attention_fa_tile_queries(int group) { return group >= 1 && 
 
 EMBER_API int ember_attention_fa(const void* q, const void* k_pool, const void* v_pool, void* out, int n_heads, int n_kv,
                                  int D, const int* tiles, int n_tiles, const int* block_table, int max_blocks, int page,
-                                 int num_pages, int window, float scale, int* err, void* stream) {
+                                 int num_pages, int window, float scale, int* err, float softcap, void* stream) {
     if (n_tiles <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail("attention_fa: bad head counts %d/%d", n_heads, n_kv);
     if (!ember_attention_fa_supported(D, n_heads / n_kv, page))
@@ -563,7 +568,9 @@ EMBER_API int ember_attention_fa(const void* q, const void* k_pool, const void* 
     FaParams p;
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table;
     p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages; p.n_heads = n_heads; p.n_kv = n_kv;
-    p.window = window; p.scale_log2 = scale * FA_LOG2E; p.n_tiles = n_tiles; p.err = err;
+    p.window = window; p.scale_log2 = scale * FA_LOG2E;
+    p.cap_over_scale = (softcap > 0.0f && scale > 0.0f) ? softcap / scale : 0.0f;
+    p.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f; p.n_tiles = n_tiles; p.err = err;
     const size_t smem = (size_t)2 * FA_ROWS * 128 + (size_t)(FA_K_STAGES + FA_V_STAGES) * 2 * FA_KT * 128 + 256;
     static bool attr = false;
     if (!attr) {

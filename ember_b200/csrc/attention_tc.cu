@@ -48,6 +48,7 @@ struct AttnTcParams {
     int n_heads, n_kv;
     int window;
     float scale_log2;         // softmax scale * log2(e)
+    float cap_log2, scale_over_cap;   // a cap on the scaled scores, cap * tanh(score / cap): cap * log2(e) and scale / cap (0: no cap)
     int n_splits, split_keys;
     int n_tiles;
     int cluster_merge;        // the splits of a tile are a thread-block cluster and are merged in its first block's shared memory
@@ -55,6 +56,11 @@ struct AttnTcParams {
 };
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// A raw score q . k as the exponent's argument in base 2: scaled, and capped where the layer has a cap.
+__device__ __forceinline__ float score_log2(const AttnTcParams& p, float raw) {
+    return p.cap_log2 > 0.0f ? p.cap_log2 * tanhf(raw * p.scale_over_cap) : raw * p.scale_log2;
+}
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -276,7 +282,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < NKG; j++) {
 #pragma unroll
-                        for (int e = 0; e < 4; e++) s[j][e] *= p.scale_log2;
+                        for (int e = 0; e < 4; e++) s[j][e] = score_log2(p, s[j][e]);
                         tmax_a = fmaxf(tmax_a, fmaxf(s[j][0], s[j][1]));
                         tmax_b = fmaxf(tmax_b, fmaxf(s[j][2], s[j][3]));
                     }
@@ -289,8 +295,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                             const bool in = key >= lo && key < hi;
                             const bool va = in && key <= qpos_a && (p.window <= 0 || key > qpos_a - p.window);
                             const bool vb2 = in && key <= qpos_b && (p.window <= 0 || key > qpos_b - p.window);
-                            s[j][e] = va ? s[j][e] * p.scale_log2 : -INFINITY;
-                            s[j][2 + e] = vb2 ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+                            s[j][e] = va ? score_log2(p, s[j][e]) : -INFINITY;
+                            s[j][2 + e] = vb2 ? score_log2(p, s[j][2 + e]) : -INFINITY;
                             tmax_a = fmaxf(tmax_a, s[j][e]);
                             tmax_b = fmaxf(tmax_b, s[j][2 + e]);
                         }
@@ -582,8 +588,9 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
                                  int n_heads, int n_kv, int D, const int* tiles, int n_tiles,
                                  const int* block_table, int max_blocks, int page, int num_pages, int window,
                                  float scale, int n_splits, int split_keys, float* part_o, float* part_ml,
-                                 int* err, void* stream) {
+                                 int* err, float softcap, void* stream) {
     if (n_tiles <= 0) return 0;
+    if (softcap < 0.0f) return fail("attention_tc: a score cap of %g", softcap);
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail("attention_tc: bad head counts %d/%d", n_heads, n_kv);
     const int G = n_heads / n_kv;
     if (!ember_attention_tc_supported(D, G, page, mode))
@@ -604,6 +611,7 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml;
     p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
     p.n_heads = n_heads; p.n_kv = n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
+    p.cap_log2 = softcap * LOG2E; p.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     p.n_splits = n_splits; p.split_keys = split_keys; p.n_tiles = n_tiles; p.err = err;
     p.cluster_merge = cluster_merge ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;

@@ -79,6 +79,9 @@ class Attention(Mixer):
                               f"{ops.ATTENTION_MAX_GROUP}")
         self.position = build_part("position", s.position)
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+        self.softcap = float(getattr(s, "softcap", 0.0))
+        if self.softcap < 0:
+            raise ConfigError("a score cap must be >= 0")
 
     # ------------------------------------------------------------------ weights
     def weight_decls(self) -> List[WeightDecl]:
@@ -197,18 +200,18 @@ class Attention(Mixer):
             if not single:
                 tiles, n = ctx.attention_tiles(tq, "all")
                 ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
-                                 self.scale, err=ctx.err, stream=ctx.stream)
+                                 self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
                 return
             if self._fa():
                 tiles, n = ctx.attention_tiles(ops.attention_fa_tile_queries(s.group), "multi")
                 if n:
                     ops.attention_fa(q, cache.k, cache.v, out, *args, tiles, n, table, cache.page_tokens, s.window,
-                                     self.scale, err=ctx.err, stream=ctx.stream)
+                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
             else:
                 tiles, n = ctx.attention_tiles(tq, "multi")
                 if n:
                     ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
-                                     self.scale, err=ctx.err, stream=ctx.stream)
+                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
             tiles, n = ctx.attention_tiles(1, "single")
             if n:
                 # Cut long key ranges only as far as it takes to keep the memory system busy: the kernel streams the
@@ -229,8 +232,11 @@ class Attention(Mixer):
                     part_o = ctx.buf_dyn("attention.part_o", n * s.num_heads * n_splits * s.head_dim, torch.float32)
                     part_ml = ctx.buf_dyn("attention.part_ml", n * s.num_heads * n_splits * 2, torch.float32)
                 ops.attention_tc(q, cache.k, cache.v, out, 1, *args, tiles, n, table, cache.page_tokens, s.window,
-                                 self.scale, n_splits, split_keys, part_o, part_ml, err=ctx.err, stream=ctx.stream)
+                                 self.scale, n_splits, split_keys, part_o, part_ml, err=ctx.err, stream=ctx.stream,
+                                 softcap=self.softcap)
             return
+        if self.softcap > 0:
+            raise ops.KernelError("attention: the general kernel has no score cap (the tensor-core kernels have)")
         tile_q = ops.attention_tile_queries(s.group)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
         # long key ranges of a small step are cut into fixed splits so that more SMs share them

@@ -99,6 +99,16 @@ class SinkAttention(_SinkSoftmax):
         self.position = build_part("position", s.position)
         # the general preparation kernel serves whatever the whole-projection one does not know
         self.general = (s.qk_norm == "head" or s.position.kind != "none" or s.q_temp_every > 0)
+        # Plain causal softmax over keys and values of equal size (no sink, window, chunk or gate) is what the engine's
+        # TMA-fed kernels compute (tcgen05 for prompt portions, mma.sync with key splits for single tokens): where they
+        # take the geometry, a bfloat16 step goes to them (``load`` decides, once the dtype and the page size are known)
+        self.dense = None
+        if (not s.sink and s.window == 0 and s.chunk == 0 and not s.head_gate and s.value_dim == s.head_dim
+                and s.head_dim % 2 == 0 and s.num_heads // s.num_kv_heads <= ops.ATTENTION_MAX_GROUP):
+            from ..config.spec import AttentionSpec
+            from .attention import Attention
+            self.dense = Attention(AttentionSpec(hidden_size=s.hidden_size, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
+                                                 head_dim=s.head_dim, softmax_scale=s.scale, softcap=s.softcap))
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
@@ -137,6 +147,13 @@ class SinkAttention(_SinkSoftmax):
         self.sink = f32("sink") if s.sink else None
         self.taps = torch.cat([f32(n + ".conv") for n in "qkv"], dim=0).contiguous() if s.conv_taps > 0 else None
         self.inv_freq, self.rotary = self.position.rotary_table(rt)
+        if self.dense is not None:
+            self.dense.rt = rt
+            multi, single = self.dense._tc_modes()
+            if not (self.DENSE_KERNELS and single and (multi or self.dense._fa())):
+                self.dense = None
+
+    DENSE_KERNELS = True        # tests switch it off to run such layers on this file's own kernels
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
@@ -156,7 +173,10 @@ class SinkAttention(_SinkSoftmax):
         group = self.spec.num_heads // self.spec.num_kv_heads
         keys = [(ops.sink_attention_tile_queries(group), "all")]
         tc = (ops.shared_row_attention_tc_tile_queries(group), "all")
-        return keys + ([tc] if tc not in keys else [])
+        keys += [tc] if tc not in keys else []
+        if self.dense is not None and getattr(self.dense, "rt", None) is not None:
+            keys += [k for k in self.dense.tile_requests() if k not in keys]
+        return keys
 
     def forward(self, ctx, x, out, cache, owns_cache: bool = True, accumulate: bool = True) -> None:
         s, rt, T, mt = self.spec, self.rt, ctx.T, ctx.max_tokens
@@ -186,8 +206,12 @@ class SinkAttention(_SinkSoftmax):
             ops.whole_norm_store(qkv, self.bias, self.q_norm_w, self.k_norm_w, s.qk_norm_eps, T, H, G, D, V, ctx.positions,
                                  ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
                                  stream=ctx.stream)
-        self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
-                     s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=proj if s.head_gate else None, head_gate_col=self.channels)
+        if self.dense is not None and getattr(self.dense, "rt", None) is not None and ops.TC_ENABLED:
+            self.dense.attend(ctx, q, cache, table, att)
+        else:
+            self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
+                         s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=proj if s.head_gate else None,
+                         head_gate_col=self.channels)
         self.o(ctx, att, out, T, ops.EPI_ADD_F32 if accumulate else ops.EPI_STORE_F32)
 
 

@@ -222,6 +222,24 @@ def test_attention_alone(dtype, heads, kv, dim, vdim, hidden, softcap, q_temp, a
     assert _rel(_run_mixer(spec, w, x, dtype), want) < MIX_TOL[dtype]
 
 
+@pytest.mark.parametrize("dense", [True, False], ids=["TMA-fed kernels", "shared-row kernels"])
+@pytest.mark.parametrize("heads,kv,dim,softcap,q_temp", [(8, 1, 128, 25.0, (0.4, 30)), (4, 2, 64, 0.0, (1.0, 9)), (16, 1, 64, 3.0, None),
+                                                         (2, 2, 128, 0.7, None)])
+def test_plain_causal_layers_on_the_engines_dense_attention_kernels(dense, heads, kv, dim, softcap, q_temp, monkeypatch):
+    """Keys and values of one size, 64 or 128, without window, chunk or gate: bfloat16 steps go to the kernels Qwen3's
+    attention uses (tcgen05 for prompt portions of 128-wide heads, the TMA-fed kernel with key splits for single tokens),
+    which take the cap as a parameter; switched off, the same layer runs on the shared-row kernels.  Portions of 130 and
+    60 tokens, then single tokens beside another request."""
+    from ember_b200.parts.sink_attention import SinkAttention
+    monkeypatch.setattr(SinkAttention, "DENSE_KERNELS", dense)
+    spec = _attention_spec(heads, kv, dim, dim, 128, 0.6, softcap, q_temp)
+    w = _weights(spec, seed=heads)
+    x = torch.randn(200, 128, generator=torch.Generator().manual_seed(2)).bfloat16()
+    want = _plain_mixer(plain.attention_mixer, x, w, _attention_m(heads, kv, dim, dim, 0.6, softcap, q_temp))
+    got = _run_mixer(spec, w, x, torch.bfloat16, portions=((130, 3), (60, 20), (1, 1), (1, 1), (1, 0 + 1), (7, 2)))
+    assert _rel(got, want) < MIX_TOL[torch.bfloat16]
+
+
 def test_the_cap_and_the_temperature_are_there():
     """Scores of about +-12 under a cap of 3: without the cap the softmax is nearly one-hot, with it nearly flat among the
     larger scores.  A temperature period of 50: positions 48 and 49 differ by the factor 1 + ln 2."""
