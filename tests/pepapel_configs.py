@@ -49,14 +49,15 @@ def _parallel(left, right, mlp):
 
 PEPAPEL = {
     # widths the tensor-core kernels take; chunks of 40 (not a multiple of a page of 16), a partial rotation, a
-    # temperature that changes every 24 positions, values wider than keys, identity experts, three groups of which two stay
+    # temperature that changes every 24 positions, values wider than keys, identity experts, three groups of which two stay;
+    # the last layer's keys and values are both 64 wide (in bfloat16 it runs on the kernels Qwen3's attention uses)
     "a": dict(seed=3, json={
         "architecture": "Pepapel", "vocab": 320, "width": 128, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0}, "postln_alpha": 1.7,
         "layers": [
             _parallel(_left(4, 2, 32, 16, 0.18, 3, 40, 16, 10000.0, 4.0), _right(4, 2, 16, 32, 2), _dense(96, 1.2)),
             {"type": "attention", "mixer": _attention(4, 1, 32, 48, 0.2, softcap=20.0, q_temp=(0.4, 24)), "mlp": _moe(48, 4, 2, identity=2, groups=(3, 2))},
             _parallel(_left(2, 2, 64, 64, 0.125, 4, 33, 64, 500.0), _right(2, 1, 32, 64, 4), _moe(32, 6, 3, groups=(2, 1))),
-            {"type": "attention", "mixer": _attention(8, 2, 16, 16, 0.3), "mlp": None},
+            {"type": "attention", "mixer": _attention(4, 2, 64, 64, 0.15, softcap=6.0), "mlp": None},
         ]}),
     # a width no tensor-core product takes; odd head sizes; one head; a convolution of one tap (no carried rows) and one
     # of five; a chunk of one page exactly; as many choices as router outputs; a single choice; a cap that binds; no
