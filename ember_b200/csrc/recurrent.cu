@@ -22,23 +22,42 @@ __device__ __forceinline__ float logsigmoidf_(float x) { return fminf(x, 0.0f) -
 // ------------------------------------------------------------------------------- short causal convolution + silu
 // out[t, c] = silu(bias[c] + sum_j taps[c, j] * in(t - (n - 1 - j), c)) (or, silu = 0, the sum itself); inputs before the run come from the
 // request's carried inputs carry[slot][j][c] (j = 0 the oldest of n - 1), zeros for a new request.
+constexpr int CONV_MAX_TAPS = 8;  // taps the kernel keeps in registers; longer filters read them from memory
+
 __global__ void conv_silu_kernel(const float* __restrict__ x, int ldx, int c0, const float* __restrict__ taps,
                                  const float* __restrict__ bias, int n, const float* __restrict__ carry, long long carry_stride,
                                  const int* __restrict__ seq_of, const int* __restrict__ query_start,
-                                 const int* __restrict__ slots, float* __restrict__ out, int C, int silu) {
+                                 const int* __restrict__ slots, float* __restrict__ out, int C, int silu, int T, int tt) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = blockIdx.y * tt,          // a block walks tt tokens: its taps and bias are read once for all of them
+               c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= C) return;
-    const int s = seq_of[t], first = query_start[s];
-    const float* cs = carry + (size_t)slots[s] * carry_stride;
-    float acc = bias ? bias[c] : 0.0f;
-    for (int j = 0; j < n; j++) {
-        const int src = t - (n - 1 - j);
-        const float v = src >= first ? x[(size_t)src * ldx + c0 + c] : cs[(size_t)(n - 1 + src - first) * C + c];
-        acc = fmaf(taps[(size_t)c * n + j], v, acc);
+    float w[CONV_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; j++) w[j] = j < n ? taps[(size_t)c * n + j] : 0.0f;
+    const float b = bias ? bias[c] : 0.0f;
+    for (int t = t0; t < min(t0 + tt, T); t++) {
+        const int s = seq_of[t], first = query_start[s];
+        const float* cs = carry + (size_t)slots[s] * carry_stride;
+        float acc = b;
+        if (n <= CONV_MAX_TAPS) {
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; j++) {
+                if (j >= n) break;
+                const int src = t - (n - 1 - j);
+                const float v = src >= first ? x[(size_t)src * ldx + c0 + c] : cs[(size_t)(n - 1 + src - first) * C + c];
+                acc = fmaf(w[j], v, acc);
+            }
+        } else {
+            for (int j = 0; j < n; j++) {
+                const int src = t - (n - 1 - j);
+                const float v = src >= first ? x[(size_t)src * ldx + c0 + c] : cs[(size_t)(n - 1 + src - first) * C + c];
+                acc = fmaf(taps[(size_t)c * n + j], v, acc);
+            }
+        }
+        out[(size_t)t * C + c] = silu ? acc / (1.0f + expf(-acc)) : acc;
     }
-    out[(size_t)t * C + c] = silu ? acc / (1.0f + expf(-acc)) : acc;
 }
 
 // After the convolution: the request's last n - 1 inputs (from the run, or shifted down from what was carried).
@@ -847,8 +866,9 @@ EMBER_API int ember_conv_silu(const float* x, int ldx, int c0, const float* taps
     if (T > 65535 || S > 65535) return fail("conv_silu: %d tokens in %d runs are too many for one launch", T, S);
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned bx = (unsigned)((C + 127) / 128);
-    launch_kernel(conv_silu_kernel, dim3(bx, T), 128, 0, st, x, ldx, c0, taps, bias, n, (const float*)carry, carry_stride, seq_of,
-                  query_start, slots, out, C, silu);
+    const int tt = T >= 1024 ? 8 : 1;          // prompt portions: eight tokens a block; small steps keep a block a token
+    launch_kernel(conv_silu_kernel, dim3(bx, (T + tt - 1) / tt), 128, 0, st, x, ldx, c0, taps, bias, n, (const float*)carry,
+                  carry_stride, seq_of, query_start, slots, out, C, silu, T, tt);
     if (n > 1)
         launch_kernel(conv_carry_kernel, dim3(bx, S), 128, 0, st, x, ldx, c0, n, carry, carry_stride, query_start, slots, C);
     return check_launch("conv_silu");

@@ -507,3 +507,43 @@ def test_experts_of_prompt_portions_on_tensor_cores(dtype, tmp_path):
     steps = trace_portions(requests, sizes=(300, 2, 118))
     outputs, _ = replay(d, dtype, steps, 448, max_batch_tokens=512)
     assert_close(collect(steps, outputs), want, dtype, "experts on tensor cores")
+
+
+# ------------------------------------------------------------------------------------ the norm after the sum
+@pytest.mark.parametrize("centred", [True, False], ids=["layer norm", "rms norm"])
+@pytest.mark.parametrize("hidden,alpha,bias", [(64, 2.5, False), (100, 0.7, True), (2048, 1.0, True), (13000, 3.0, False)])
+def test_scale_add_norm_in_one_kernel(hidden, alpha, bias, centred):
+    """x <- norm(alpha x + y + b) in place, with the bfloat16 copy of the new rows; rows with a large mean, so that a
+    variance taken as E[x^2] - mean^2 or a missing centring would show."""
+    from ember_b200 import ops
+    g = torch.Generator().manual_seed(hidden)
+    x = (torch.randn(37, hidden, generator=g) + 30.0).cuda()
+    y = torch.randn(37, hidden, generator=g).cuda()
+    w = (1 + 0.2 * torch.randn(hidden, generator=g)).cuda()
+    b = torch.randn(hidden, generator=g).cuda() if bias else None
+    z = alpha * x.double() + y.double() + (b.double() if bias else 0.0)
+    if centred:
+        z = z - z.mean(-1, keepdim=True)
+    want = z / torch.sqrt((z * z).mean(-1, keepdim=True) + 1e-5) * w.double()
+    rounded = torch.zeros(40, hidden, dtype=torch.bfloat16, device="cuda")
+    keep = x[30:].clone()
+    ops.scaled_add_norm(y, b, alpha, w, None, 1e-5, centred, x, 30, rounded=rounded)
+    torch.cuda.synchronize()
+    assert float((x[:30].double() - want[:30]).abs().max()) < 2e-5 * float(want.abs().max())
+    assert torch.equal(rounded[:30], x[:30].bfloat16()) and torch.equal(x[30:], keep) and float(rounded[30:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("hidden", [64, 100, 2048])
+def test_two_rows_normed_weighed_and_summed_in_one_kernel(hidden):
+    from ember_b200 import ops
+    g = torch.Generator().manual_seed(hidden)
+    a, b = (100.0 * torch.randn(20, hidden, generator=g)).cuda(), (0.01 * torch.randn(20, hidden, generator=g)).cuda()
+    wa, wb = (1 + 0.2 * torch.randn(hidden, generator=g)).cuda(), torch.randn(hidden, generator=g).cuda()
+    rms = lambda t: t.double() / torch.sqrt((t.double() ** 2).mean(-1, keepdim=True) + 1e-6)      # noqa: E731
+    want = rms(a) * wa.double() + rms(b) * wb.double()
+    out = torch.full((20, hidden), 3.0, device="cuda")
+    ops.pair_norm_sum(a, wa, b, wb, 1e-6, out, 16)
+    ops.pair_norm_sum(a, wa, b, wb, 1e-6, out, 16, accumulate=True)
+    torch.cuda.synchronize()
+    assert float((out[:16].double() - 2 * want[:16]).abs().max()) < 1e-5 * float(want.abs().max())
+    assert float((out[16:] - 3.0).abs().max()) == 0.0
