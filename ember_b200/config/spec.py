@@ -113,6 +113,7 @@ class AttentionSpec(PartSpec):
     softmax_scale: Optional[float] = None   # None = 1/sqrt(head_dim)
     position: PartSpec = field(default_factory=NoPositionSpec)
     softcap: float = 0.0          # > 0: score <- softcap * tanh(score / softcap) after the scale (tensor-core kernels only)
+    chunk: int = 0                # > 0: position i sees j <= i only if floor(i / chunk) == floor(j / chunk) (tensor-core kernels only)
 
     @property
     def q_dim(self) -> int:

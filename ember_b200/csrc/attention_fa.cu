@@ -55,6 +55,7 @@ struct FaParams {
     int max_blocks, page, num_pages;
     int n_heads, n_kv;
     int window;
+    int chunk;                // > 0: a query sees a key only inside its own chunk of positions (chunks counted from position 0)
     float scale_log2;
     float cap_over_scale, scale_over_cap;   // a cap on the scaled scores, cap * tanh(scale s / cap), applied to the raw scores as (cap / scale) tanh(s scale / cap); 0: no cap
     int n_tiles;
@@ -201,7 +202,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
               pos0 = p.tiles[tile * 4 + 3];
     const int G = p.n_heads / p.n_kv;
     const int rows = nq * G;
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = max(p.window > 0 ? max(0, pos0 - p.window + 1) : 0, p.chunk > 0 ? pos0 - pos0 % p.chunk : 0);
     const int hi = pos0 + nq;
     const int k_begin = lo - (lo % FA_KT);
     const int n_kt = hi > k_begin ? (hi - k_begin + FA_KT - 1) / FA_KT : 0;
@@ -391,14 +392,16 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
 
             const bool interior = k0 >= lo && k0 + FA_KT <= hi && k0 + FA_KT - 1 <= pos0 &&
-                                  (p.window <= 0 || k0 > pos0 + (rows - 1) / G - p.window);
+                                  (p.window <= 0 || k0 > pos0 + (rows - 1) / G - p.window) &&
+                                  (p.chunk <= 0 || k0 >= (pos0 + (rows - 1) / G) - (pos0 + (rows - 1) / G) % p.chunk);
             // the maximum is taken over the raw scores; the scale (> 0) is folded into the exponent below
             float tmax;
             if (!interior) {
 #pragma unroll
                 for (int i = 0; i < FA_KT; i++) {
                     const int key = k0 + i;
-                    const bool vis = key >= lo && key < hi && key <= qpos && (p.window <= 0 || key > qpos - p.window);
+                    const bool vis = key >= lo && key < hi && key <= qpos && (p.window <= 0 || key > qpos - p.window) &&
+                                     (p.chunk <= 0 || key >= qpos - qpos % p.chunk);
                     s[i] = vis ? s[i] : -INFINITY;
                 }
             }
@@ -555,7 +558,7 @@ EMBER_API int ember_attention_fa_tile_queries(int group) { return group >= 1 && 
 
 EMBER_API int ember_attention_fa(const void* q, const void* k_pool, const void* v_pool, void* out, int n_heads, int n_kv,
                                  int D, const int* tiles, int n_tiles, const int* block_table, int max_blocks, int page,
-                                 int num_pages, int window, float scale, int* err, float softcap, void* stream) {
+                                 int num_pages, int window, float scale, int* err, float softcap, int chunk, void* stream) {
     if (n_tiles <= 0) return 0;
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail("attention_fa: bad head counts %d/%d", n_heads, n_kv);
     if (!ember_attention_fa_supported(D, n_heads / n_kv, page))
@@ -568,7 +571,7 @@ EMBER_API int ember_attention_fa(const void* q, const void* k_pool, const void* 
     FaParams p;
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table;
     p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages; p.n_heads = n_heads; p.n_kv = n_kv;
-    p.window = window; p.scale_log2 = scale * FA_LOG2E;
+    p.window = window; p.chunk = chunk < 0 ? 0 : chunk; p.scale_log2 = scale * FA_LOG2E;
     p.cap_over_scale = (softcap > 0.0f && scale > 0.0f) ? softcap / scale : 0.0f;
     p.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f; p.n_tiles = n_tiles; p.err = err;
     const size_t smem = (size_t)2 * FA_ROWS * 128 + (size_t)(FA_K_STAGES + FA_V_STAGES) * 2 * FA_KT * 128 + 256;

@@ -47,6 +47,7 @@ struct AttnTcParams {
     int max_blocks, page, num_pages;
     int n_heads, n_kv;
     int window;
+    int chunk;                // > 0: a query sees a key only inside its own chunk of positions (chunks counted from position 0)
     float scale_log2;         // softmax scale * log2(e)
     float cap_log2, scale_over_cap;   // a cap on the scaled scores, cap * tanh(score / cap): cap * log2(e) and scale / cap (0: no cap)
     int n_splits, split_keys;
@@ -148,7 +149,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int G = p.n_heads / p.n_kv;
     const int rows = nq * G;
 
-    int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    int lo = max(p.window > 0 ? max(0, pos0 - p.window + 1) : 0, p.chunk > 0 ? pos0 - pos0 % p.chunk : 0);
     int hi = pos0 + nq;
     if (p.n_splits > 1) {
         lo = max(lo, split * p.split_keys);
@@ -277,7 +278,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 float tmax_a = -INFINITY, tmax_b = -INFINITY;
                 const int first_q = pos0 + min(wrow, rows - 1) / G;          // earliest query position of this warp
                 const bool interior = k0 + koff >= lo && k0 + koff + NKG * 8 <= hi && k0 + koff + NKG * 8 - 1 <= first_q &&
-                                      (p.window <= 0 || k0 + koff > warp_last_q - p.window);
+                                      (p.window <= 0 || k0 + koff > warp_last_q - p.window) &&
+                                      (p.chunk <= 0 || k0 + koff >= warp_last_q - warp_last_q % p.chunk);
                 if (interior) {
 #pragma unroll
                     for (int j = 0; j < NKG; j++) {
@@ -293,8 +295,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         for (int e = 0; e < 2; e++) {
                             const int key = k0 + koff + j * 8 + 2 * t4 + e;
                             const bool in = key >= lo && key < hi;
-                            const bool va = in && key <= qpos_a && (p.window <= 0 || key > qpos_a - p.window);
-                            const bool vb2 = in && key <= qpos_b && (p.window <= 0 || key > qpos_b - p.window);
+                            const bool va = in && key <= qpos_a && (p.window <= 0 || key > qpos_a - p.window) &&
+                                            (p.chunk <= 0 || key >= qpos_a - qpos_a % p.chunk);
+                            const bool vb2 = in && key <= qpos_b && (p.window <= 0 || key > qpos_b - p.window) &&
+                                             (p.chunk <= 0 || key >= qpos_b - qpos_b % p.chunk);
                             s[j][e] = va ? score_log2(p, s[j][e]) : -INFINITY;
                             s[j][2 + e] = vb2 ? score_log2(p, s[j][2 + e]) : -INFINITY;
                             tmax_a = fmaxf(tmax_a, s[j][e]);
@@ -588,7 +592,7 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
                                  int n_heads, int n_kv, int D, const int* tiles, int n_tiles,
                                  const int* block_table, int max_blocks, int page, int num_pages, int window,
                                  float scale, int n_splits, int split_keys, float* part_o, float* part_ml,
-                                 int* err, float softcap, void* stream) {
+                                 int* err, float softcap, int chunk, void* stream) {
     if (n_tiles <= 0) return 0;
     if (softcap < 0.0f) return fail("attention_tc: a score cap of %g", softcap);
     if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv) return fail("attention_tc: bad head counts %d/%d", n_heads, n_kv);
@@ -610,7 +614,7 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     AttnTcParams p;
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml;
     p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
-    p.n_heads = n_heads; p.n_kv = n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
+    p.n_heads = n_heads; p.n_kv = n_kv; p.window = window; p.chunk = chunk < 0 ? 0 : chunk; p.scale_log2 = scale * LOG2E;
     p.cap_log2 = softcap * LOG2E; p.scale_over_cap = softcap > 0.0f ? scale / softcap : 0.0f;
     p.n_splits = n_splits; p.split_keys = split_keys; p.n_tiles = n_tiles; p.err = err;
     p.cluster_merge = cluster_merge ? 1 : 0;

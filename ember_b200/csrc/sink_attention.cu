@@ -190,6 +190,18 @@ __global__ void __launch_bounds__(256) head_prepare_store_kernel(HeadPrepareArgs
     }
 }
 
+// x[t, h, :] *= sigmoid(gate[t, h]) for an attention result x [T, H, DV]: the gate per head as a pass of its own, behind
+// attention kernels that do not take it.
+template <typename T>
+__global__ void head_gate_apply_kernel(T* __restrict__ x, const float* __restrict__ gate, int ld_gate, int H, int DV, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const size_t th = i / DV;
+    x[i] = from_float<T>(to_float(x[i]) * sigmoidf_(gate[(th / H) * (size_t)ld_gate + th % H]));
+}
+
 // ------------------------------------------------------------------------------------- latents of a token
 struct LatentArgs {
     const float* a; int ld;            // [T, ...] fp32: the fused down-projections
@@ -1052,6 +1064,18 @@ EMBER_API int ember_head_prepare_store(const float* qkv, int ld, const float* bi
     else if (dtype == EMBER_BF16) launch_kernel(head_prepare_store_kernel<__nv_bfloat16>, T_tokens, 256, smem, st, p);
     else return fail("head_prepare_store: unsupported dtype %d", dtype);
     return check_launch("head_prepare_store");
+}
+
+EMBER_API int ember_head_gate_apply(void* x, int dtype, const float* gate, int ld_gate, int T_tokens, int H, int DV, void* stream) {
+    if (T_tokens <= 0) return 0;
+    if (H <= 0 || DV <= 0 || ld_gate < H) return fail("head_gate_apply: %d heads of %d, gate rows of %d", H, DV, ld_gate);
+    const size_t n = (size_t)T_tokens * H * DV;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == EMBER_F32) launch_kernel(head_gate_apply_kernel<float>, (unsigned)((n + 255) / 256), 256, 0, st, (float*)x, gate, ld_gate, H, DV, n);
+    else if (dtype == EMBER_BF16)
+        launch_kernel(head_gate_apply_kernel<__nv_bfloat16>, (unsigned)((n + 255) / 256), 256, 0, st, (__nv_bfloat16*)x, gate, ld_gate, H, DV, n);
+    else return fail("head_gate_apply: unsupported dtype %d", dtype);
+    return check_launch("head_gate_apply");
 }
 
 EMBER_API int ember_latent_prepare(const float* a, int ld, int q_col, int q_rank, int c_col, int kv_rank, int rot_dim,

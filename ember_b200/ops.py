@@ -511,9 +511,10 @@ def attention_fa_tile_queries(group: int) -> int:
 def attention_fa(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int,
                  n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor, page: int,
                  window: int, scale: float, err: Optional[torch.Tensor] = None, stream: Optional[int] = None,
-                 softcap: float = 0.0) -> None:
+                 softcap: float = 0.0, chunk: int = 0) -> None:
     """bf16 causal attention of prompt portions on tcgen05 tensor cores (S and O in tensor memory).  ``softcap`` > 0: the
-    scaled score becomes softcap * tanh(score / softcap)."""
+    scaled score becomes softcap * tanh(score / softcap); ``chunk`` > 0: position i sees j only if
+    floor(i / chunk) == floor(j / chunk)."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(k_pool, "k_pool", torch.bfloat16)
@@ -525,15 +526,17 @@ def attention_fa(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ou
     lib = _lib("attention_fa")
     _call(lib, lib.ember_attention_fa, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(n_heads), c_int(n_kv), c_int(head_dim),
           _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]),
-          c_int(window), c_float(scale), _p(err), c_float(softcap), c_void_p(stream if stream is not None else current_stream_ptr()))
+          c_int(window), c_float(scale), _p(err), c_float(softcap), c_int(chunk),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, mode: int,
                  n_heads: int, n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor,
                  page: int, window: int, scale: float, n_splits: int = 1, split_keys: int = 0,
                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
-                 err: Optional[torch.Tensor] = None, stream: Optional[int] = None, softcap: float = 0.0) -> None:
-    """bf16 attention over the paged cache on tensor cores (TMA-fed); ``softcap`` > 0 caps the scaled scores by a tanh.  ``mode`` 0 takes tiles of
+                 err: Optional[torch.Tensor] = None, stream: Optional[int] = None, softcap: float = 0.0, chunk: int = 0) -> None:
+    """bf16 attention over the paged cache on tensor cores (TMA-fed); ``softcap`` > 0 caps the scaled scores by a tanh,
+    ``chunk`` > 0 lets position i see j only if floor(i / chunk) == floor(j / chunk).  ``mode`` 0 takes tiles of
     prompt portions, 1 takes single-token tiles and may split their key range: with ``part_o`` / ``part_ml`` the
     splits' partial results go through those buffers and a second kernel merges them; without them (at most 8
     splits) the splits of a tile are a thread-block cluster and are merged in shared memory."""
@@ -554,7 +557,7 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ou
     _call(lib, lib.ember_attention_tc, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(mode), c_int(n_heads), c_int(n_kv),
           c_int(head_dim), _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]), c_int(page),
           c_int(k_pool.shape[0]), c_int(window), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o),
-          _p(part_ml), _p(err), c_float(softcap), c_void_p(stream if stream is not None else current_stream_ptr()))
+          _p(part_ml), _p(err), c_float(softcap), c_int(chunk), c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
 # ------------------------------------------------ norms and gates around a sublayer (csrc/norm_gate.cu)
@@ -1042,6 +1045,17 @@ def _check_head_gate(head_gate, T: int, heads: int, col: int = 0) -> None:
         _check(head_gate, "head_gate", torch.float32)
         if head_gate.dim() != 2 or head_gate.shape[0] < T or col < 0 or head_gate.shape[1] < col + heads:
             raise KernelError(f"attention: a head gate of {tuple(head_gate.shape)} from column {col} for {T} tokens of {heads} heads")
+
+
+def head_gate_apply(x: torch.Tensor, gate: torch.Tensor, gate_col: int, T: int, heads: int, vdim: int, stream: Optional[int] = None) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, gate_col + h]) in place (x [T, heads vdim] bfloat16 or float32, gate fp32 logits)."""
+    _check(x, "x")
+    _check_head_gate(gate, T, heads, gate_col)
+    if gate is None or x.numel() < T * heads * vdim:
+        raise KernelError("head_gate_apply: buffers do not fit the step")
+    lib = _lib("sink_attention")
+    _call(lib, lib.ember_head_gate_apply, _p(x), c_int(dtype_code(x.dtype)), _off(gate, gate_col), c_int(gate.shape[-1]), c_int(T),
+          c_int(heads), c_int(vdim), _stream(stream))
 
 
 def head_prepare_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], norm_mode: str, q_w: Optional[torch.Tensor],

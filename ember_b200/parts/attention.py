@@ -80,8 +80,9 @@ class Attention(Mixer):
         self.position = build_part("position", s.position)
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
         self.softcap = float(getattr(s, "softcap", 0.0))
-        if self.softcap < 0:
-            raise ConfigError("a score cap must be >= 0")
+        self.chunk = int(getattr(s, "chunk", 0))
+        if self.softcap < 0 or self.chunk < 0 or (self.chunk > 0 and s.window > 0):
+            raise ConfigError("a score cap and a chunk must be >= 0, and a chunk excludes a window")
 
     # ------------------------------------------------------------------ weights
     def weight_decls(self) -> List[WeightDecl]:
@@ -200,18 +201,18 @@ class Attention(Mixer):
             if not single:
                 tiles, n = ctx.attention_tiles(tq, "all")
                 ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
-                                 self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
+                                 self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap, chunk=self.chunk)
                 return
             if self._fa():
                 tiles, n = ctx.attention_tiles(ops.attention_fa_tile_queries(s.group), "multi")
                 if n:
                     ops.attention_fa(q, cache.k, cache.v, out, *args, tiles, n, table, cache.page_tokens, s.window,
-                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
+                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap, chunk=self.chunk)
             else:
                 tiles, n = ctx.attention_tiles(tq, "multi")
                 if n:
                     ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
-                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap)
+                                     self.scale, err=ctx.err, stream=ctx.stream, softcap=self.softcap, chunk=self.chunk)
             tiles, n = ctx.attention_tiles(1, "single")
             if n:
                 # Cut long key ranges only as far as it takes to keep the memory system busy: the kernel streams the
@@ -225,7 +226,7 @@ class Attention(Mixer):
                 # 3 splits: 1.895 -> 1.805 ms a step; one request at 3,072: 12 splits through buffers 1.351 ms, 8 in a
                 # cluster 1.305 ms; at 32,768 the 16 splits through buffers win, 28.5 against 42.9 us a layer).
                 n_splits, split_keys, in_cluster = plan_decode_splits(
-                    n, ctx.max_context, s.window, s.num_kv_heads, s.head_dim, ops.num_sms(q.device),
+                    n, ctx.max_context, s.window or self.chunk, s.num_kv_heads, s.head_dim, ops.num_sms(q.device),
                     ops.ATTENTION_CLUSTER_SPLITS if self.CLUSTER_MERGE else 0, self.MERGE_KERNEL_US, self.CACHE_BYTES_PER_US)
                 part_o = part_ml = None
                 if n_splits > 1 and not in_cluster:
@@ -233,10 +234,10 @@ class Attention(Mixer):
                     part_ml = ctx.buf_dyn("attention.part_ml", n * s.num_heads * n_splits * 2, torch.float32)
                 ops.attention_tc(q, cache.k, cache.v, out, 1, *args, tiles, n, table, cache.page_tokens, s.window,
                                  self.scale, n_splits, split_keys, part_o, part_ml, err=ctx.err, stream=ctx.stream,
-                                 softcap=self.softcap)
+                                 softcap=self.softcap, chunk=self.chunk)
             return
-        if self.softcap > 0:
-            raise ops.KernelError("attention: the general kernel has no score cap (the tensor-core kernels have)")
+        if self.softcap > 0 or self.chunk > 0:
+            raise ops.KernelError("attention: the general kernel has no score cap and no chunks (the tensor-core kernels have)")
         tile_q = ops.attention_tile_queries(s.group)
         tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
         # long key ranges of a small step are cut into fixed splits so that more SMs share them

@@ -99,16 +99,17 @@ class SinkAttention(_SinkSoftmax):
         self.position = build_part("position", s.position)
         # the general preparation kernel serves whatever the whole-projection one does not know
         self.general = (s.qk_norm == "head" or s.position.kind != "none" or s.q_temp_every > 0)
-        # Plain causal softmax over keys and values of equal size (no sink, window, chunk or gate) is what the engine's
-        # TMA-fed kernels compute (tcgen05 for prompt portions, mma.sync with key splits for single tokens): where they
-        # take the geometry, a bfloat16 step goes to them (``load`` decides, once the dtype and the page size are known)
+        # Causal softmax over keys and values of equal size (no sink, no window; a cap and chunks are parameters) is what
+        # the engine's TMA-fed kernels compute (tcgen05 for prompt portions, mma.sync with key splits for single tokens):
+        # where they take the geometry, a bfloat16 step goes to them (``load`` decides, once the dtype and the page size
+        # are known); a gate per head then is a pass of its own behind them
         self.dense = None
-        if (not s.sink and s.window == 0 and s.chunk == 0 and not s.head_gate and s.value_dim == s.head_dim
+        if (not s.sink and s.window == 0 and s.value_dim == s.head_dim
                 and s.head_dim % 2 == 0 and s.num_heads // s.num_kv_heads <= ops.ATTENTION_MAX_GROUP):
             from ..config.spec import AttentionSpec
             from .attention import Attention
             self.dense = Attention(AttentionSpec(hidden_size=s.hidden_size, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
-                                                 head_dim=s.head_dim, softmax_scale=s.scale, softcap=s.softcap))
+                                                 head_dim=s.head_dim, softmax_scale=s.scale, softcap=s.softcap, chunk=s.chunk))
 
     def weight_decls(self) -> List[WeightDecl]:
         s, p = self.spec, self.prefix
@@ -208,6 +209,8 @@ class SinkAttention(_SinkSoftmax):
                                  stream=ctx.stream)
         if self.dense is not None and getattr(self.dense, "rt", None) is not None and ops.TC_ENABLED:
             self.dense.attend(ctx, q, cache, table, att)
+            if s.head_gate:
+                ops.head_gate_apply(att, proj, self.channels, T, H, V, stream=ctx.stream)
         else:
             self._attend(ctx, q, cache.k, cache.v, att, table, cache.page_tokens, H, G, D, V, s.window, s.keep_first, self.sink,
                          s.scale, chunk=s.chunk, softcap=s.softcap, head_gate=proj if s.head_gate else None,

@@ -240,6 +240,27 @@ def test_plain_causal_layers_on_the_engines_dense_attention_kernels(dense, heads
     assert _rel(got, want) < MIX_TOL[torch.bfloat16]
 
 
+@pytest.mark.parametrize("dense", [True, False], ids=["TMA-fed kernels", "shared-row kernels"])
+@pytest.mark.parametrize("heads,kv,dim,taps,chunk,rot", [(8, 1, 128, 4, 50, {"dims": 64, "base": 1e4, "scaling": {"factor": 4.0}}),
+                                                        (4, 2, 64, 2, 64, {"dims": 64, "base": 500.0}),
+                                                        (2, 2, 128, 3, 7, {"dims": 16, "base": 1e6}),
+                                                        (4, 4, 64, 1, 300, {"dims": 32, "base": 1e4})])
+def test_chunked_layers_on_the_engines_dense_attention_kernels(dense, heads, kv, dim, taps, chunk, rot, monkeypatch):
+    """Left halves whose keys and values are one size, 64 or 128: the same kernels take the chunk as a second lower bound
+    on the visible keys, the gate per head follows as a pass of its own.  Chunks that end inside a 130-token portion, at
+    a key tile's edge (64), every seven positions, and never (300); then single tokens across an edge."""
+    from ember_b200.parts.sink_attention import SinkAttention
+    monkeypatch.setattr(SinkAttention, "DENSE_KERNELS", dense)
+    spec = _left_spec(heads, kv, dim, dim, 128, taps, chunk, rot, scale=0.5)
+    w = _weights(spec, seed=heads, std=0.15)
+    x = torch.randn(200, 128, generator=torch.Generator().manual_seed(8)).bfloat16()
+    want = _plain_mixer(plain.chunked_attention_mixer, x, w, _left_m(heads, kv, dim, dim, taps, chunk, rot, 0.5))
+    got = _run_mixer(spec, w, x, torch.bfloat16, portions=((130, 3), (60, 20), (1, 1), (1, 1), (1, 1), (7, 2)))
+    assert _rel(got, want) < MIX_TOL[torch.bfloat16]
+    for t in (49, 50, 51, 63, 64, 65, 127, 128, 129, 130, 189, 190, 191, 192, 193, 199):
+        assert _rel(got[t], want[t]) < 3 * MIX_TOL[torch.bfloat16], t
+
+
 def test_the_cap_and_the_temperature_are_there():
     """Scores of about +-12 under a cap of 3: without the cap the softmax is nearly one-hot, with it nearly flat among the
     larger scores.  A temperature period of 50: positions 48 and 49 differ by the factor 1 + ln 2."""
